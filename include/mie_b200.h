@@ -1,0 +1,174 @@
+/*
+ * mie_b200 — C-ABI of the B200 (sm_100a) continuous-batching hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and element strides, a
+ * CUDA stream handle and (where metadata is read on the device) a pointer to
+ * an int32 status word in device memory.  No entry point allocates device
+ * memory unless its comment says so, none synchronises the stream, and all of
+ * them may be captured into a CUDA graph.
+ *
+ * Return value: 0 on success, a negative MIE_ERR_* code when the arguments
+ * are rejected on the host (nothing was launched; mie_last_error() holds a
+ * message).  Problems that only the device can see (a page id outside the
+ * pool, a length that overruns its block table, a wait that ran out) never
+ * trap: the offending row is skipped or clamped and a MIE_STATUS_* bit is
+ * OR-ed into *status, which the caller reads back with its next device→host
+ * copy.
+ *
+ * The reference engine has no FFI: its boundary is Python functions over
+ * torch tensors (paths below are relative to the reference project).  Each
+ * declaration cites the Python function whose launch it replaces; the Python
+ * package mini_inference_engine_b200.engine re-exports those functions with
+ * the reference's names and signatures and calls this library through ctypes.
+ */
+#ifndef MIE_B200_H_
+#define MIE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MIE_OK 0
+#define MIE_ERR_INVALID_ARGUMENT (-1)
+#define MIE_ERR_CUDA (-2)
+#define MIE_ERR_UNSUPPORTED (-3)
+
+/* Bits OR-ed into the device status word. */
+#define MIE_STATUS_BAD_LENGTH 1      /* sequence length < 1 or beyond the block-table capacity */
+#define MIE_STATUS_BAD_POSITION 2    /* query position outside [0, length) */
+#define MIE_STATUS_BAD_PAGE 4        /* live block-table entry outside [0, num_blocks) */
+#define MIE_STATUS_BAD_SEQUENCE 8    /* token_to_sequence entry outside the block-table rows */
+#define MIE_STATUS_WAIT_TIMEOUT 16   /* a bounded device-side wait gave up */
+#define MIE_STATUS_MAX_LENGTH 32     /* attention read length beyond max_sequence_length */
+#define MIE_STATUS_CAPACITY 64       /* work plan did not fit the scratch the caller sized */
+
+/* Element types of K/V pages, queries and activations. */
+#define MIE_DTYPE_BF16 0
+#define MIE_DTYPE_F16 1
+#define MIE_DTYPE_F32 2
+
+/* An int32 or int64 metadata tensor (1-D or 2-D) with element strides. */
+typedef struct {
+  const void* ptr;
+  int32_t is64;
+  int64_t stride0;
+  int64_t stride1;
+} mie_index_t;
+
+/* A 4-D tensor view: base pointer and element strides. */
+typedef struct {
+  void* ptr;
+  int64_t stride[4];
+} mie_view4_t;
+
+const char* mie_last_error(void);
+int mie_version(void);
+/* Number of SMs of the current device (used by callers to size scratch). */
+int mie_sm_count(void);
+
+/* ------------------------------------------------------------------------
+ * KV-cache scatter
+ * ---------------------------------------------------------------------- */
+
+/*
+ * Replaces triton_write_decode_kv (engine/kv_cache/triton_paged_kv.py:154-223,
+ * kernel :20-107): for every request b and KV head h copy the one new K and V
+ * row to page block_tables[b][pos / block_size], slot pos % block_size, where
+ * pos = query_positions[b] if given, else sequence_lengths[b] - 1.
+ * key_states / value_states: [batch, kv_heads, 1, head_dim] with independent
+ * strides.  key_blocks / value_blocks: [num_blocks, kv_heads, block_size,
+ * head_dim].  A bit-exact copy.
+ */
+int mie_write_decode_kv(mie_view4_t key_states, mie_view4_t value_states, mie_index_t block_tables,
+                        mie_index_t sequence_lengths, mie_index_t query_positions /* ptr may be NULL */,
+                        mie_view4_t key_blocks, mie_view4_t value_blocks, int32_t batch, int32_t kv_heads,
+                        int32_t head_dim, int32_t block_size, int32_t num_blocks, int32_t table_width,
+                        int32_t elem_bytes, int32_t* status, void* stream);
+
+/*
+ * Replaces triton_write_packed_kv (engine/kv_cache/triton_packed_kv.py:146-208,
+ * kernel :18-104): scatter `tokens` packed rows; row t goes to sequence
+ * token_to_sequence[t], position token_positions[t], i.e. slot
+ * block_tables[seq][pos / block_size] * block_size + pos % block_size.
+ * key_states / value_states: [1, kv_heads, tokens, head_dim], V with strides
+ * of its own.
+ */
+int mie_write_packed_kv(mie_view4_t key_states, mie_view4_t value_states, mie_index_t token_to_sequence,
+                        mie_index_t token_positions, mie_index_t block_tables, mie_view4_t key_blocks,
+                        mie_view4_t value_blocks, int32_t tokens, int32_t kv_heads, int32_t head_dim,
+                        int32_t block_size, int32_t num_blocks, int32_t table_rows, int32_t table_width,
+                        int32_t elem_bytes, int32_t* status, void* stream);
+
+/*
+ * Replaces PagedKvCache.gather_layer (engine/kv_cache/paged.py:910-944) and the
+ * index_select gather of engine/kv_cache/qwen3_paged.py:296-312 ("block-table
+ * gather"): copies the first `length` tokens of one sequence out of its pages
+ * into dense [kv_heads, length, head_dim] K and V (contiguous).  Bit-exact.
+ */
+int mie_gather_kv(mie_view4_t key_blocks, mie_view4_t value_blocks, mie_index_t block_table_row,
+                  void* key_out, void* value_out, int32_t length, int32_t kv_heads, int32_t head_dim,
+                  int32_t block_size, int32_t num_blocks, int32_t elem_bytes, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Decode metadata validation
+ * ---------------------------------------------------------------------- */
+
+/*
+ * Replaces the device half of validate_decode_metadata
+ * (engine/kv_cache/decode_metadata.py:67-91).  The reference turns the checks
+ * into device asserts under graph capture; here one small kernel applies the
+ * same predicates and ORs MIE_STATUS_* bits into *status, so a bad replay is
+ * reported without losing the context.  reserved_lengths (host array, may be
+ * NULL) is only checked by the Python shim in eager mode.
+ */
+int mie_validate_decode_metadata(mie_index_t block_tables, mie_index_t sequence_lengths,
+                                 mie_index_t query_positions /* ptr may be NULL */, int32_t batch,
+                                 int32_t table_width, int32_t block_size, int32_t num_blocks,
+                                 int64_t max_sequence_length /* <=0: unchecked */, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Paged decode attention
+ * ---------------------------------------------------------------------- */
+
+/*
+ * Bytes of scratch (work plan + split-KV partials) that
+ * mie_paged_decode_attention needs for a batch whose attention read lengths
+ * sum to at most max_total_tokens.  Host arithmetic only.
+ */
+int64_t mie_decode_scratch_bytes(int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                                 int64_t max_total_tokens);
+
+/*
+ * Replaces triton_paged_decode_attention
+ * (engine/kv_cache/triton_paged_attention.py:680-974; kernels :28, :181, :314,
+ * :480) and tensor_core_decode_attention (engine/kv_cache/triton_tc_decode.py:177).
+ *
+ * query [batch, q_heads, 1, head_dim], out [batch, q_heads, 1, head_dim] (any
+ * strides, last dim contiguous), pages [num_blocks, kv_heads, block_size,
+ * head_dim].  Row b attends to the first min(len[b], pos[b]+1) tokens (len[b]
+ * if query_positions.ptr is NULL).
+ *
+ * split_policy: 0 = one work item per (request, KV head) (no split-KV);
+ *               1 = length-proportional split-KV chosen on the device from the
+ *                   batch's total length (the partials are merged by a second
+ *                   kernel); > 1 = fixed chunk of that many tokens (multiple of 16).
+ * scratch: device buffer of at least mie_decode_scratch_bytes(...) bytes,
+ * 256-byte aligned; contents need not be initialised.  plan_only / use_plan
+ * let a model step build the work plan once (layer 0) and reuse it for the
+ * other layers: plan_only=1 builds the plan and returns; use_plan=1 skips the
+ * plan kernel and uses slot `plan_slot` (0..63) of the plan's work counters.
+ */
+int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mie_view4_t key_blocks,
+                               mie_view4_t value_blocks, mie_index_t block_tables, mie_index_t sequence_lengths,
+                               mie_index_t query_positions /* ptr may be NULL */, int32_t batch, int32_t q_heads,
+                               int32_t kv_heads, int32_t head_dim, int32_t block_size, int32_t num_blocks,
+                               int32_t table_width, int32_t dtype, float scale, int32_t split_policy,
+                               int64_t max_total_tokens, void* scratch, int64_t scratch_bytes, int32_t plan_only,
+                               int32_t use_plan, int32_t plan_slot, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MIE_B200_H_ */

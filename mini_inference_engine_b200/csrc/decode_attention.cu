@@ -1,0 +1,676 @@
+// Ragged-batch paged decode attention for sm_100a.
+//
+// Fast path (bf16/fp16, head_dim 128, page size a multiple of 16, GQA group <= 8):
+//   * a tiny plan kernel cuts every request's context into length-proportional
+//     chunks (split-KV) and lists (request, chunk) work items;
+//   * the main kernel is persistent: 8 autonomous warps per SM each pull
+//     (request, chunk, KV head) items from a device counter, stream that item's
+//     K/V pages HBM -> shared memory with TMA (16-token boxes, 128-byte
+//     swizzle, a private 3-stage mbarrier ring per warp, no multicast), and
+//     compute Q.K^T and P.V for all query heads that share the KV head with
+//     mma.sync, so each K/V byte is read from HBM once per group; softmax is
+//     online in fp32 with quad shuffles;
+//   * a merge kernel combines the chunks of requests that were split.
+// Everything else takes a generic one-warp-per-(request, head) kernel.
+//
+// The op is HBM-bound (4 FLOP per KV byte at GQA 4:1), so the MMA shape padding
+// (4 real query rows of 16) costs nothing that matters.
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace mie {
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kStages = 3;
+constexpr int kTileTokens = 16;
+constexpr int kHeadDim = 128;
+constexpr int kTileBytes = kTileTokens * kHeadDim * 2;  // one K or V tile
+constexpr int kStageBytes = 2 * kTileBytes;             // K + V
+constexpr int kPidBatch = 128;                          // tiles whose page ids are staged at once
+constexpr int kMinChunk = 64;
+constexpr int kMaxChunk = 2048;
+constexpr int kPlanThreads = 1024;
+constexpr int kHeaderInts = 128;  // [0]=chunk [1]=seq_chunks [2]=items; [16..79] work counters
+constexpr int kCounterBase = 16;
+constexpr int kCounters = 64;
+
+struct View4 {
+  char* ptr;
+  long long s[4];
+  __host__ View4(const mie_view4_t& v) : ptr(reinterpret_cast<char*>(v.ptr)) {
+    for (int i = 0; i < 4; ++i) s[i] = v.stride[i];
+  }
+};
+
+struct Scratch {
+  int* header;
+  int* offsets;     // [batch + 1]
+  int* item_seq;    // [cap]
+  int* item_chunk;  // [cap]
+  float* part_m;    // [cap][q_heads]
+  float* part_l;    // [cap][q_heads]
+  float* part_o;    // [cap][q_heads][head_dim]
+  int cap;
+};
+
+__host__ __device__ inline long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
+
+// Attention read length of request b, or 0 (with a status bit) when the
+// metadata is unusable.
+__device__ __forceinline__ long long read_length(const IndexView& lengths, const IndexView& positions, int b,
+                                                 long long capacity, int* status) {
+  const long long len = lengths.at(b);
+  if (len < 1 || len > capacity) {
+    raise_status(status, MIE_STATUS_BAD_LENGTH);
+    return 0;
+  }
+  if (!positions.valid()) return len;
+  const long long pos = positions.at(b);
+  if (pos < 0) {
+    raise_status(status, MIE_STATUS_BAD_POSITION);
+    return 0;
+  }
+  return pos + 1 < len ? pos + 1 : len;
+}
+
+// ---------------------------------------------------------------------------
+// Plan kernel: one CTA.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ long long block_sum_ll(long long v, long long* smem) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  long long t = 0;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += smem[i];
+  __syncthreads();
+  return t;
+}
+
+__global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, IndexView positions, int batch,
+                                                            long long capacity_tokens, int kv_heads, int policy,
+                                                            int target_seq_chunks, Scratch sc, int* status) {
+  __shared__ long long red[32];
+  __shared__ int warp_tot[32];
+  __shared__ int running_s;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+  long long local = 0;
+  for (int b = tid; b < batch; b += blockDim.x) local += read_length(lengths, positions, b, capacity_tokens, status);
+  const long long total = block_sum_ll(local, red);
+
+  long long chunk;
+  if (policy == 0) {
+    chunk = (1ll << 40);
+  } else if (policy == 1) {
+    chunk = (total + target_seq_chunks - 1) / target_seq_chunks;
+    chunk = align_up(chunk, kTileTokens);
+    if (chunk < kMinChunk) chunk = kMinChunk;
+    if (chunk > kMaxChunk) chunk = kMaxChunk;
+  } else {
+    chunk = align_up(policy, kTileTokens);
+  }
+  // Never emit more (request, chunk) pairs than the caller's scratch holds.
+  const long long room = sc.cap - batch;  // > 0, checked on the host
+  if (total / chunk + batch > sc.cap) {
+    chunk = align_up((total + room - 1) / room, kTileTokens);  // still exact, only coarser
+  }
+
+  if (tid == 0) running_s = 0;
+  __syncthreads();
+  for (int base = 0; base < batch; base += blockDim.x) {
+    const int b = base + tid;
+    int c = 0;
+    if (b < batch) {
+      const long long rl = read_length(lengths, positions, b, capacity_tokens, nullptr);
+      c = (int)((rl + chunk - 1) / chunk);
+    }
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int before = running_s;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    const int excl = before + incl - c;
+    if (b < batch) {
+      sc.offsets[b] = excl;
+      for (int j = 0; j < c; ++j) {
+        sc.item_seq[excl + j] = b;
+        sc.item_chunk[excl + j] = j;
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int t = 0;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += warp_tot[w];
+      running_s += t;
+    }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    sc.offsets[batch] = running_s;
+    sc.header[0] = (int)(chunk > 0x7fffffffll ? 0x7fffffff : chunk);
+    sc.header[1] = running_s;
+    sc.header[2] = running_s * kv_heads;
+  }
+  if (tid < kCounters) sc.header[kCounterBase + tid] = 0;
+}
+
+// ---------------------------------------------------------------------------
+// Main kernel
+// ---------------------------------------------------------------------------
+struct DecodeParams {
+  View4 q, out;
+  IndexView tables, lengths, positions;
+  Scratch sc;
+  int batch, q_heads, kv_heads, group, block_size, num_blocks, table_width;
+  float scale_log2;
+  int counter_slot;
+  int* status;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32, 1)
+    decode_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                  const DecodeParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(align_up((long long)reinterpret_cast<uintptr_t>(smem_raw), 1024));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* stages = smem + (size_t)warp * kStages * kStageBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * kStages * kStageBytes) + warp * kStages;
+  int* pids = reinterpret_cast<int*>(smem + (size_t)kWarps * kStages * kStageBytes + kWarps * kStages * 8) +
+              warp * kPidBatch;
+
+  if (lane == 0) {
+    for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&kmap);
+    tma_prefetch_desc(&vmap);
+  }
+  __syncthreads();
+
+  const int g = lane >> 2, t = lane & 3;
+  const int chunk = p.sc.header[0];
+  const int total_items = p.sc.header[2];
+  int* counter = p.sc.header + kCounterBase + p.counter_slot;
+  const long long capacity_tokens = (long long)p.table_width * p.block_size;
+  uint32_t parity = 0;
+
+  // ldmatrix lane geometry (constant per lane).
+  const int k_tok = (lane & 7) + ((lane >> 4) & 1) * 8, k_sel = (lane >> 3) & 1;
+  const int v_tok = (lane & 7) + ((lane >> 3) & 1) * 8, v_sel = (lane >> 4) & 1;
+  const uint32_t k_row = k_tok * 128, k_key = k_tok & 7;
+  const uint32_t v_row = v_tok * 128, v_key = v_tok & 7;
+
+  while (true) {
+    int item = 0;
+    if (lane == 0) item = atomicAdd(counter, 1);
+    item = __shfl_sync(0xffffffffu, item, 0);
+    if (item >= total_items) break;
+    const int sci = item / p.kv_heads, h = item % p.kv_heads;
+    const int b = p.sc.item_seq[sci], ck = p.sc.item_chunk[sci];
+    const long long rl = read_length(p.lengths, p.positions, b, capacity_tokens, nullptr);
+    const int nchunks = p.sc.offsets[b + 1] - p.sc.offsets[b];
+    const long long t_begin = (long long)ck * chunk;
+    const long long t_end = rl < t_begin + chunk ? rl : t_begin + chunk;
+    const int ntiles = (int)((t_end - t_begin + kTileTokens - 1) / kTileTokens);
+
+    // Query fragments: rows g < group are real heads, the rest of the 16 MMA rows are zero.
+    uint32_t qa[8][2];
+    {
+      const bool real = g < p.group;
+      const T* qrow = reinterpret_cast<const T*>(p.q.ptr) + (long long)b * p.q.s[0] +
+                      (long long)(h * p.group + (real ? g : 0)) * p.q.s[1];
+#pragma unroll
+      for (int ks = 0; ks < 8; ++ks) {
+        const uint32_t lo = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * t);
+        const uint32_t hi = *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * t);
+        qa[ks][0] = real ? lo : 0u;
+        qa[ks][1] = real ? hi : 0u;
+      }
+    }
+
+    float m = -INFINITY, l = 0.f;
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+    bool timed_out = false;
+    for (int batch0 = 0; batch0 < ntiles && !timed_out; batch0 += kPidBatch) {
+      const int nb = ntiles - batch0 < kPidBatch ? ntiles - batch0 : kPidBatch;
+      __syncwarp();
+      for (int i = lane; i < nb; i += 32) {
+        const long long tok = t_begin + (long long)(batch0 + i) * kTileTokens;
+        long long pid = p.tables.at(b, tok / p.block_size);
+        if (pid < 0 || pid >= p.num_blocks) {
+          raise_status(p.status, MIE_STATUS_BAD_PAGE);
+          pid = 0;
+        }
+        pids[i] = (int)pid;
+      }
+      __syncwarp();
+      auto issue = [&](int i) {
+        const int s = i % kStages;
+        const long long tok = t_begin + (long long)(batch0 + i) * kTileTokens;
+        const int tok_in_page = (int)(tok % p.block_size);
+        uint8_t* dst = stages + (size_t)s * kStageBytes;
+        mbar_expect_tx(&bars[s], kStageBytes);
+        tma_load_4d(dst, &kmap, &bars[s], 0, tok_in_page, h, pids[i]);
+        tma_load_4d(dst + kTileBytes / 2, &kmap, &bars[s], 64, tok_in_page, h, pids[i]);
+        tma_load_4d(dst + kTileBytes, &vmap, &bars[s], 0, tok_in_page, h, pids[i]);
+        tma_load_4d(dst + kTileBytes + kTileBytes / 2, &vmap, &bars[s], 64, tok_in_page, h, pids[i]);
+      };
+      if (lane == 0) {
+        for (int i = 0; i < kStages && i < nb; ++i) issue(i);
+      }
+      for (int i = 0; i < nb; ++i) {
+        const int s = i % kStages;
+        const bool arrived = mbar_wait_bounded(&bars[s], (parity >> s) & 1u);
+        if (!__all_sync(0xffffffffu, arrived)) {
+          timed_out = true;
+          break;
+        }
+        parity ^= 1u << s;
+        const uint32_t kbase = smem_u32(stages + (size_t)s * kStageBytes);
+        const uint32_t vbase = kbase + kTileBytes;
+        const long long tok0 = t_begin + (long long)(batch0 + i) * kTileTokens;
+        const int valid = (int)(t_end - tok0 < kTileTokens ? t_end - tok0 : kTileTokens);
+
+        if (valid < kTileTokens) {
+          // Rows past the read length may hold anything (even NaN bits): zero
+          // them in V so that 0 * V stays 0.  K rows are masked by select below.
+          uint8_t* vt = stages + (size_t)s * kStageBytes + kTileBytes;
+          for (int c = lane; c < 2 * kTileTokens * 8; c += 32) {
+            const int half = c / (kTileTokens * 8), rem = c % (kTileTokens * 8);
+            const int row = rem / 8;
+            if (row >= valid) {
+              *reinterpret_cast<uint4*>(vt + half * (kTileBytes / 2) + row * 128 + (rem % 8) * 16) =
+                  make_uint4(0, 0, 0, 0);
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+        }
+
+        // S = Q K^T for 16 tokens: two n-tiles, two accumulator sets to shorten the chain.
+        float sa[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float sb[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t addr =
+              kbase + (ks >> 2) * (kTileBytes / 2) + k_row + (((((ks & 3) * 2) | k_sel) ^ k_key) << 4);
+          uint32_t r0, r1, r2, r3;
+          ldmatrix_x4(r0, r1, r2, r3, addr);
+          if (ks & 1) {
+            Mma16816<T>::run(sb[0], qa[ks][0], 0u, qa[ks][1], 0u, r0, r1);
+            Mma16816<T>::run(sb[1], qa[ks][0], 0u, qa[ks][1], 0u, r2, r3);
+          } else {
+            Mma16816<T>::run(sa[0], qa[ks][0], 0u, qa[ks][1], 0u, r0, r1);
+            Mma16816<T>::run(sa[1], qa[ks][0], 0u, qa[ks][1], 0u, r2, r3);
+          }
+        }
+        // This lane's four scores of head g: tokens 2t, 2t+1, 8+2t, 9+2t.
+        float sv[4];
+        sv[0] = (sa[0][0] + sb[0][0]) * p.scale_log2;
+        sv[1] = (sa[0][1] + sb[0][1]) * p.scale_log2;
+        sv[2] = (sa[1][0] + sb[1][0]) * p.scale_log2;
+        sv[3] = (sa[1][1] + sb[1][1]) * p.scale_log2;
+        const int tk = 2 * t;
+        if (tk >= valid) sv[0] = -INFINITY;
+        if (tk + 1 >= valid) sv[1] = -INFINITY;
+        if (tk + 8 >= valid) sv[2] = -INFINITY;
+        if (tk + 9 >= valid) sv[3] = -INFINITY;
+        float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m, mx);  // finite: token 0 of a tile is always valid
+        const float alpha = exp2f(m - m_new);
+        const float p0 = exp2f(sv[0] - m_new), p1 = exp2f(sv[1] - m_new);
+        const float p2 = exp2f(sv[2] - m_new), p3 = exp2f(sv[3] - m_new);
+        l = l * alpha + ((p0 + p1) + (p2 + p3));
+        m = m_new;
+        const uint32_t pa0 = Mma16816<T>::pack(p0, p1), pa2 = Mma16816<T>::pack(p2, p3);
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          o[n][0] *= alpha;
+          o[n][1] *= alpha;
+        }
+        // O += P V
+#pragma unroll
+        for (int np = 0; np < 8; ++np) {
+          const uint32_t addr =
+              vbase + (np >> 2) * (kTileBytes / 2) + v_row + (((((np & 3) * 2) | v_sel) ^ v_key) << 4);
+          uint32_t r0, r1, r2, r3;
+          ldmatrix_x4_trans(r0, r1, r2, r3, addr);
+          Mma16816<T>::run(o[2 * np], pa0, 0u, pa2, 0u, r0, r1);
+          Mma16816<T>::run(o[2 * np + 1], pa0, 0u, pa2, 0u, r2, r3);
+        }
+        __syncwarp();
+        if (lane == 0 && i + kStages < nb) issue(i + kStages);
+      }
+    }
+    if (timed_out) {
+      if (lane == 0) raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+      break;
+    }
+
+    // Row sum over the quad, then write the result (final or partial).
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (g < p.group) {
+      const int head = h * p.group + g;
+      if (nchunks == 1) {
+        const float inv = 1.f / fmaxf(l, 1.17549435e-38f);
+        T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)b * p.out.s[0] + (long long)head * p.out.s[1];
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          *reinterpret_cast<uint32_t*>(orow + n * 8 + 2 * t) = Mma16816<T>::pack(o[n][0] * inv, o[n][1] * inv);
+        }
+      } else {
+        const long long row = (long long)(p.sc.offsets[b] + ck) * p.q_heads + head;
+        float* po = p.sc.part_o + row * kHeadDim;
+#pragma unroll
+        for (int n = 0; n < 16; ++n) {
+          *reinterpret_cast<float2*>(po + n * 8 + 2 * t) = make_float2(o[n][0], o[n][1]);
+        }
+        if (t == 0) {
+          p.sc.part_m[row] = m;
+          p.sc.part_l[row] = l;
+        }
+      }
+    }
+  }
+}
+
+// Merge the chunks of split requests; also zero-fills rows with nothing to read.
+template <typename T>
+__global__ void __launch_bounds__(kHeadDim) merge_kernel(DecodeParams p) {
+  const int b = blockIdx.x / p.q_heads, head = blockIdx.x % p.q_heads;
+  const int first = p.sc.offsets[b], n = p.sc.offsets[b + 1] - first;
+  if (n == 1) return;
+  const int d = threadIdx.x;
+  T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)b * p.out.s[0] + (long long)head * p.out.s[1];
+  if (n == 0) {
+    orow[d] = from_float<T>(0.f);
+    return;
+  }
+  float mmax = -INFINITY;
+  for (int i = 0; i < n; ++i) mmax = fmaxf(mmax, p.sc.part_m[(long long)(first + i) * p.q_heads + head]);
+  float acc = 0.f, lsum = 0.f;
+  for (int i = 0; i < n; ++i) {
+    const long long row = (long long)(first + i) * p.q_heads + head;
+    const float w = exp2f(p.sc.part_m[row] - mmax);
+    lsum += p.sc.part_l[row] * w;
+    acc += p.sc.part_o[row * kHeadDim + d] * w;
+  }
+  orow[d] = from_float<T>(acc / fmaxf(lsum, 1.17549435e-38f));
+}
+
+// ---------------------------------------------------------------------------
+// Generic kernel: any head_dim <= 1024, any page size, bf16/fp16/fp32.
+// One warp per (request, query head); lanes split head_dim.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void generic_decode_kernel(View4 q, View4 out, View4 kb, View4 vb, IndexView tables, IndexView lengths,
+                                      IndexView positions, int batch, int q_heads, int kv_heads, int head_dim,
+                                      int block_size, int num_blocks, int table_width, float scale, int* status) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (warp >= batch * q_heads) return;
+  const int b = warp / q_heads, head = warp % q_heads;
+  const int kvh = head / (q_heads / kv_heads);
+  constexpr int kMaxPerLane = 32;
+  const int per_lane = (head_dim + 31) / 32;
+  float qv[kMaxPerLane], acc[kMaxPerLane];
+  const T* qrow = reinterpret_cast<const T*>(q.ptr) + (long long)b * q.s[0] + (long long)head * q.s[1];
+#pragma unroll 4
+  for (int i = 0; i < per_lane; ++i) {
+    const int d = lane + 32 * i;
+    qv[i] = d < head_dim ? to_float<T>(qrow[(long long)d * q.s[3]]) : 0.f;
+    acc[i] = 0.f;
+  }
+  const long long rl = read_length(lengths, positions, b, (long long)table_width * block_size,
+                                   lane == 0 ? status : nullptr);
+  float m = -INFINITY, l = 0.f;
+  for (long long tok = 0; tok < rl; ++tok) {
+    const long long page = tables.at(b, tok / block_size);
+    if (page < 0 || page >= num_blocks) {
+      if (lane == 0) raise_status(status, MIE_STATUS_BAD_PAGE);
+      continue;
+    }
+    const long long slot = tok % block_size;
+    const T* krow = reinterpret_cast<const T*>(kb.ptr) + page * kb.s[0] + (long long)kvh * kb.s[1] + slot * kb.s[2];
+    const T* vrow = reinterpret_cast<const T*>(vb.ptr) + page * vb.s[0] + (long long)kvh * vb.s[1] + slot * vb.s[2];
+    float dot = 0.f;
+    for (int i = 0; i < per_lane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < head_dim) dot += qv[i] * to_float<T>(krow[(long long)d * kb.s[3]]);
+    }
+    dot = warp_sum(dot) * scale;
+    const float m_new = fmaxf(m, dot);
+    const float alpha = __expf(m - m_new), pw = __expf(dot - m_new);
+    l = l * alpha + pw;
+    for (int i = 0; i < per_lane; ++i) {
+      const int d = lane + 32 * i;
+      if (d < head_dim) acc[i] = acc[i] * alpha + pw * to_float<T>(vrow[(long long)d * vb.s[3]]);
+    }
+    m = m_new;
+  }
+  T* orow = reinterpret_cast<T*>(out.ptr) + (long long)b * out.s[0] + (long long)head * out.s[1];
+  const float inv = rl > 0 ? 1.f / fmaxf(l, 1.17549435e-38f) : 0.f;
+  for (int i = 0; i < per_lane; ++i) {
+    const int d = lane + 32 * i;
+    if (d < head_dim) orow[(long long)d * out.s[3]] = from_float<T>(acc[i] * inv);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+struct MapKey {
+  void* ptr;
+  long long s0, s1, s2;
+  int num_blocks, kv_heads, block_size, dtype;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && s0 == o.s0 && s1 == o.s1 && s2 == o.s2 && num_blocks == o.num_blocks &&
+           kv_heads == o.kv_heads && block_size == o.block_size && dtype == o.dtype;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ (size_t)k.s0;
+    h = h * 1000003u ^ (size_t)k.s1;
+    h = h * 1000003u ^ (size_t)k.s2;
+    h = h * 1000003u ^ (size_t)(k.num_blocks * 131 + k.kv_heads * 17 + k.block_size * 3 + k.dtype);
+    return h;
+  }
+};
+
+int page_tensor_map(const mie_view4_t& pages, int num_blocks, int kv_heads, int block_size, int dtype,
+                    CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key{pages.ptr, pages.stride[0], pages.stride[1], pages.stride[2], num_blocks, kv_heads, block_size, dtype};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return MIE_OK;
+    }
+  }
+  const uint64_t dims[4] = {(uint64_t)kHeadDim, (uint64_t)block_size, (uint64_t)kv_heads, (uint64_t)num_blocks};
+  const uint64_t strides[3] = {(uint64_t)pages.stride[2] * 2, (uint64_t)pages.stride[1] * 2,
+                               (uint64_t)pages.stride[0] * 2};
+  const uint32_t box[4] = {64, kTileTokens, 1, 1};
+  const int rc = make_tensor_map(out, dtype == MIE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                              : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                                 4, pages.ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MIE_OK) return rc;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 8192) cache.clear();
+  cache.emplace(key, *out);
+  return MIE_OK;
+}
+
+bool pages_fit_tma(const mie_view4_t& v, int head_dim, int block_size) {
+  if (head_dim != kHeadDim || block_size % kTileTokens != 0 || v.stride[3] != 1) return false;
+  if (reinterpret_cast<uintptr_t>(v.ptr) & 15) return false;
+  for (int i = 0; i < 3; ++i) {
+    if (v.stride[i] <= 0 || (v.stride[i] * 2) % 16 != 0) return false;
+  }
+  return true;
+}
+
+constexpr size_t kDecodeSmem = (size_t)kWarps * kStages * kStageBytes + kWarps * kStages * 8 +
+                               (size_t)kWarps * kPidBatch * 4 + 1024;
+
+long long fixed_scratch_bytes(int batch) { return kHeaderInts * 4 + align_up((long long)(batch + 1) * 4, 256); }
+long long per_chunk_bytes(int q_heads, int head_dim) { return 8 + (long long)q_heads * (head_dim + 2) * 4; }
+
+int target_seq_chunks(int kv_heads) {
+  const int items = sm_count() * kWarps * 4;
+  return (items + kv_heads - 1) / kv_heads;
+}
+
+Scratch carve(void* scratch, long long bytes, int batch, int q_heads, int head_dim) {
+  Scratch s;
+  char* base = reinterpret_cast<char*>(scratch);
+  s.header = reinterpret_cast<int*>(base);
+  s.offsets = reinterpret_cast<int*>(base + kHeaderInts * 4);
+  long long off = fixed_scratch_bytes(batch);
+  const long long avail = bytes - off - 1024;
+  long long cap = avail / per_chunk_bytes(q_heads, head_dim);
+  if (cap > 0x3fffffff) cap = 0x3fffffff;
+  s.cap = (int)(cap > 0 ? cap : 0);
+  s.item_seq = reinterpret_cast<int*>(base + off);
+  off += align_up((long long)s.cap * 4, 256);
+  s.item_chunk = reinterpret_cast<int*>(base + off);
+  off += align_up((long long)s.cap * 4, 256);
+  s.part_m = reinterpret_cast<float*>(base + off);
+  off += align_up((long long)s.cap * q_heads * 4, 256);
+  s.part_l = reinterpret_cast<float*>(base + off);
+  off += align_up((long long)s.cap * q_heads * 4, 256);
+  s.part_o = reinterpret_cast<float*>(base + off);
+  return s;
+}
+
+template <typename T>
+int launch_fast(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMap& vmap, cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  MIE_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    MIE_CUDA(cudaFuncSetAttribute(decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDecodeSmem));
+    configured[dev] = true;
+  }
+  decode_kernel<T><<<sm_count(), kWarps * 32, kDecodeSmem, stream>>>(kmap, vmap, p);
+  MIE_LAUNCH_CHECK("decode_kernel");
+  merge_kernel<T><<<p.batch * p.q_heads, kHeadDim, 0, stream>>>(p);
+  MIE_LAUNCH_CHECK("merge_kernel");
+  return MIE_OK;
+}
+
+template <typename T>
+int launch_generic(mie_view4_t query, mie_view4_t out, mie_view4_t kb, mie_view4_t vb, mie_index_t tables,
+                   mie_index_t lengths, mie_index_t positions, int batch, int q_heads, int kv_heads, int head_dim,
+                   int block_size, int num_blocks, int table_width, float scale, int* status, cudaStream_t stream) {
+  const int threads = 128;
+  const long long warps = (long long)batch * q_heads;
+  const int blocks = (int)((warps * 32 + threads - 1) / threads);
+  generic_decode_kernel<T><<<blocks, threads, 0, stream>>>(View4(query), View4(out), View4(kb), View4(vb),
+                                                          IndexView(tables), IndexView(lengths),
+                                                          IndexView(positions), batch, q_heads, kv_heads, head_dim,
+                                                          block_size, num_blocks, table_width, scale, status);
+  MIE_LAUNCH_CHECK("generic_decode_kernel");
+  return MIE_OK;
+}
+
+}  // namespace
+}  // namespace mie
+
+using namespace mie;
+
+extern "C" int64_t mie_decode_scratch_bytes(int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                                            int64_t max_total_tokens) {
+  if (batch < 0 || q_heads < 1 || kv_heads < 1 || head_dim < 1 || max_total_tokens < 0) return 0;
+  // (request, chunk) pairs never exceed batch + min(target, total / min_chunk) + total / max_chunk.
+  long long aimed = target_seq_chunks(kv_heads);
+  if (max_total_tokens / kMinChunk + 1 < aimed) aimed = max_total_tokens / kMinChunk + 1;
+  const long long cap = (long long)batch + aimed + max_total_tokens / kMaxChunk + 2;
+  return fixed_scratch_bytes(batch) + cap * per_chunk_bytes(q_heads, head_dim) + 8 * 256 + 1024;
+}
+
+extern "C" int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mie_view4_t key_blocks,
+                                          mie_view4_t value_blocks, mie_index_t block_tables,
+                                          mie_index_t sequence_lengths, mie_index_t query_positions, int32_t batch,
+                                          int32_t q_heads, int32_t kv_heads, int32_t head_dim, int32_t block_size,
+                                          int32_t num_blocks, int32_t table_width, int32_t dtype, float scale,
+                                          int32_t split_policy, int64_t max_total_tokens, void* scratch,
+                                          int64_t scratch_bytes, int32_t plan_only, int32_t use_plan,
+                                          int32_t plan_slot, int32_t* status, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MIE_CHECK_ARG(batch >= 0 && q_heads >= 1 && kv_heads >= 1 && q_heads % kv_heads == 0,
+                "query heads (%d) must be a positive multiple of KV heads (%d)", q_heads, kv_heads);
+  MIE_CHECK_ARG(head_dim >= 1 && head_dim <= 1024, "head_dim must be in [1, 1024], got %d", head_dim);
+  MIE_CHECK_ARG(block_size >= 1 && num_blocks >= 1 && table_width >= 1, "invalid page geometry");
+  MIE_CHECK_ARG(dtype == MIE_DTYPE_BF16 || dtype == MIE_DTYPE_F16 || dtype == MIE_DTYPE_F32, "unknown dtype %d",
+                dtype);
+  MIE_CHECK_ARG(query.ptr && out.ptr && key_blocks.ptr && value_blocks.ptr && block_tables.ptr &&
+                    sequence_lengths.ptr,
+                "null tensor pointer");
+  MIE_CHECK_ARG(split_policy >= 0, "split_policy must be >= 0");
+  MIE_CHECK_ARG(plan_slot >= 0 && plan_slot < kCounters, "plan_slot must be in [0, %d)", kCounters);
+  (void)max_total_tokens;
+  if (batch == 0) return MIE_OK;
+
+  const int group = q_heads / kv_heads;
+  const bool fast = dtype != MIE_DTYPE_F32 && group <= 8 && pages_fit_tma(key_blocks, head_dim, block_size) &&
+                    pages_fit_tma(value_blocks, head_dim, block_size) && query.stride[3] == 1 &&
+                    out.stride[3] == 1 && query.stride[0] % 2 == 0 && query.stride[1] % 2 == 0 &&
+                    out.stride[0] % 2 == 0 && out.stride[1] % 2 == 0 &&
+                    (reinterpret_cast<uintptr_t>(query.ptr) & 3) == 0 &&
+                    (reinterpret_cast<uintptr_t>(out.ptr) & 3) == 0 && scratch != nullptr;
+  if (!fast) {
+    MIE_CHECK_ARG(!plan_only && !use_plan, "work plans exist only for the TMA decode path");
+    if (dtype == MIE_DTYPE_BF16)
+      return launch_generic<__nv_bfloat16>(query, out, key_blocks, value_blocks, block_tables, sequence_lengths,
+                                           query_positions, batch, q_heads, kv_heads, head_dim, block_size,
+                                           num_blocks, table_width, scale, status, stream);
+    if (dtype == MIE_DTYPE_F16)
+      return launch_generic<__half>(query, out, key_blocks, value_blocks, block_tables, sequence_lengths,
+                                    query_positions, batch, q_heads, kv_heads, head_dim, block_size, num_blocks,
+                                    table_width, scale, status, stream);
+    return launch_generic<float>(query, out, key_blocks, value_blocks, block_tables, sequence_lengths,
+                                 query_positions, batch, q_heads, kv_heads, head_dim, block_size, num_blocks,
+                                 table_width, scale, status, stream);
+  }
+
+  MIE_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 255) == 0, "scratch must be 256-byte aligned");
+  Scratch sc = carve(scratch, scratch_bytes, batch, q_heads, head_dim);
+  MIE_CHECK_ARG(sc.cap > batch, "scratch of %lld bytes is too small for batch %d", (long long)scratch_bytes, batch);
+
+  DecodeParams p{View4(query), View4(out), IndexView(block_tables), IndexView(sequence_lengths),
+                 IndexView(query_positions), sc, batch, q_heads, kv_heads, group, block_size, num_blocks,
+                 table_width, scale * 1.4426950408889634f, plan_slot, status};
+  if (!use_plan) {
+    plan_kernel<<<1, kPlanThreads, 0, stream>>>(p.lengths, p.positions, batch, (long long)table_width * block_size,
+                                                kv_heads, split_policy, target_seq_chunks(kv_heads), sc, status);
+    MIE_LAUNCH_CHECK("plan_kernel");
+  }
+  if (plan_only) return MIE_OK;
+
+  CUtensorMap kmap, vmap;
+  if (int rc = page_tensor_map(key_blocks, num_blocks, kv_heads, block_size, dtype, &kmap)) return rc;
+  if (int rc = page_tensor_map(value_blocks, num_blocks, kv_heads, block_size, dtype, &vmap)) return rc;
+  if (dtype == MIE_DTYPE_BF16) return launch_fast<__nv_bfloat16>(p, kmap, vmap, stream);
+  return launch_fast<__half>(p, kmap, vmap, stream);
+}
