@@ -168,6 +168,39 @@ int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mie_view4_t k
                                int64_t max_total_tokens, void* scratch, int64_t scratch_bytes, int32_t plan_only,
                                int32_t use_plan, int32_t plan_slot, int32_t* status, void* stream);
 
+/* ------------------------------------------------------------------------
+ * FP8 128x128 block-scaled linear
+ * ---------------------------------------------------------------------- */
+
+/*
+ * Replaces quantize_sm89_fp8_activation (engine/kernels/sm89_fp8.py:401-424,
+ * kernel :303-332): per token and per 128-column group, scale = amax / 448 (the
+ * RAW scale is stored, 0 for an all-zero group), q = x / max(scale, 1e-12)
+ * rounded to e4m3.  x [m, k] (row stride ldx elements), q [m, k] bytes (row
+ * stride ldq).  The scales are written K-group major: scales[group * scale_ld +
+ * token], scale_ld >= m, which is the layout mie_fp8_gemm reads.
+ */
+int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t ldq, float* scales,
+                     int32_t scale_ld, int32_t m, int32_t k, void* stream);
+
+/* Bytes of workspace mie_fp8_gemm needs.  The first 262144 bytes (tile counters)
+ * must be zero before the first launch; every launch leaves them zero. */
+int64_t mie_fp8_gemm_workspace_bytes(int32_t m, int32_t n, int32_t k);
+
+/*
+ * Replaces the GEMM of sm89_fp8_linear (engine/kernels/sm89_fp8.py:444-528;
+ * kernels _fp8_linear_kernel :220-300 and _fp8_split_gemm_kernel :343-398):
+ *   y[m, n] = sum_kb dot(x8[m, kb], w8[n, kb]) * a_scale[kb][m] * w_scale[n / 128][kb]
+ * with fp32 accumulation and K blocks in increasing order, y in bf16 or fp16.
+ * x8 [m, k] e4m3 (row stride ldx bytes), a_scale as mie_fp8_quantize writes it,
+ * w8 [n, k] e4m3 (row stride ldw bytes), w_scale [ceil(n/128), w_scale_ld].
+ * Operand base pointers and row strides must be multiples of 16 bytes.
+ */
+int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
+                 int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy, int32_t out_dtype,
+                 int32_t m, int32_t n, int32_t k, void* workspace, int64_t workspace_bytes, int32_t* status,
+                 void* stream);
+
 #ifdef __cplusplus
 }
 #endif

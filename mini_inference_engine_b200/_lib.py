@@ -65,6 +65,12 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                                   c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                                   c_float, c_int32, c_int64, c_void_p, c_int64, c_int32, c_int32,
                                                   c_int32, c_void_p, c_void_p]),
+    "mie_fp8_quantize": (ctypes.c_int, [c_void_p, c_int64, c_int32, c_void_p, c_int64, c_void_p, c_int32, c_int32,
+                                        c_int32, c_void_p]),
+    "mie_fp8_gemm_workspace_bytes": (c_int64, [c_int32, c_int32, c_int32]),
+    "mie_fp8_gemm": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_int32,
+                                    c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_int64,
+                                    c_void_p, c_void_p]),
 }
 
 _lib: ctypes.CDLL | None = None

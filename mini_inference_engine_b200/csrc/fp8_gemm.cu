@@ -1,0 +1,634 @@
+// FP8 (e4m3 x e4m3) GEMM with 128x128 weight-block scales and per-token
+// per-128-column activation scales, fp32 accumulation, bf16/fp16 output:
+//
+//   Y[m, n] = sum_kb ( sum_{k in kb} X8[m, k] * W8[n, k] ) * a_scale[m, kb] * w_scale[n / 128, kb]
+//
+// sm_100a design
+//   * tcgen05.mma kind::f8f6f4 (UMMA 128 x BN x 32), operands staged in shared
+//     memory by TMA (2-D tiled loads, 128-byte swizzle, no multicast), fp32
+//     accumulators in tensor memory.
+//   * The scales change every 128 columns of K, so each K block is accumulated
+//     in its own TMEM buffer (two buffers, ping-pong) and the epilogue warps
+//     promote it into fp32 registers with that block's scale (tcgen05.ld +
+//     FFMA) while the tensor core already works on the next block.
+//   * Warp roles: E epilogue warps (E = 4 or 8), one TMA producer warp, one
+//     MMA-issuer warp that also owns the TMEM allocation.
+//   * Two orientations share the kernel.  "Normal" (many tokens): the 128 UMMA
+//     rows are tokens, the BN columns are weight rows.  "Swapped" (few tokens,
+//     decode): the 128 UMMA rows are weight rows and the BN columns are tokens,
+//     so a handful of tokens still fills the tensor core's M and the kernel is
+//     a pure weight-streaming (HBM-bound) loop.
+//   * Persistent stream-K schedule: the (tile, K block) iteration space is cut
+//     into gridDim.x equal contiguous ranges, so every SM streams the same
+//     number of bytes whatever the shape.  A CTA that owns only part of a
+//     tile's K range writes an fp32 partial; the last contributor to arrive
+//     (an atomic ticket, never a spin) sums the partials in a fixed order, so
+//     results are deterministic.
+//   * Every mbarrier wait is bounded; a wait that runs out sets
+//     MIE_STATUS_WAIT_TIMEOUT, the roles fall through to the common exit and
+//     TMEM is released.
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace mie {
+namespace {
+
+constexpr int kTileR = 128;  // UMMA M
+constexpr int kBlockK = 128; // bytes of K per pipeline stage = one scale block
+constexpr int kUmmaK = 32;   // fp8 elements per tcgen05.mma
+constexpr int kCounterInts = 1 << 16;  // tile counters at the front of the workspace
+
+// --------------------------------------------------------------------------
+// tcgen05 wrappers
+// --------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte-swizzled shared-memory operand descriptor: rows are 128
+// bytes apart, 8-row groups 1024 bytes apart (the layout a 128-byte-wide TMA
+// box with SWIZZLE_128B writes).
+__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);  // start address
+  d |= (uint64_t)1 << 16;                       // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
+  d |= (uint64_t)1 << 46;                       // descriptor version (Blackwell)
+  d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: D fp32, A/B e4m3, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t instr_desc_f8(int bn) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | (0u << 16) | ((uint32_t)(bn >> 3) << 17) |
+         ((uint32_t)(kTileR >> 4) << 24);
+}
+
+__device__ __forceinline__ void epi_bar_sync(int threads) {
+  asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");
+}
+
+// --------------------------------------------------------------------------
+// Kernel
+// --------------------------------------------------------------------------
+struct GemmParams {
+  // Row operand rows / column operand rows (see the orientation note above).
+  int rows_r, rows_c, k;
+  int m, n;               // logical problem (tokens, weight rows)
+  const float* a_scale;   // [k_blocks][a_scale_ld]  (token scales, K-block major)
+  int a_scale_ld;
+  const float* w_scale;   // [ceil(n/128)][w_scale_ld]
+  int w_scale_ld;
+  void* y;                // [m][ldy] bf16 or fp16
+  long long ldy;
+  int out_f16;
+  float* workspace;       // [2 * gridDim.x][BN][128] fp32 partial tiles
+  int* tile_counters;     // [tiles], zero between launches
+  int* status;
+};
+
+template <int BN, int E>
+struct GemmSmem {
+  static constexpr int kStageBytes = kTileR * kBlockK + BN * kBlockK;
+  static constexpr int kStages = (200 * 1024 / kStageBytes) > 12 ? 12 : (200 * 1024 / kStageBytes);
+  static constexpr int kBarBytes = (2 * kStages + 4) * 8;
+  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 2 * BN * 4 + 64 + 1024;
+};
+
+template <int BN, int E, bool kSwap>
+__global__ void __launch_bounds__((E + 2) * 32, 1)
+    fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_c,
+                    const GemmParams p) {
+  using S = GemmSmem<BN, E>;
+  constexpr int kStages = S::kStages;
+  constexpr int kCols = E == 8 ? BN / 2 : BN;  // accumulator columns owned by one epilogue warp
+  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
+  static_assert(kCols % 16 == 0, "column slice must be a multiple of 16");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  float* svec = reinterpret_cast<float*>(tmem_empty + 2);  // [2][BN] combined scales (swapped mode)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(svec + 2 * BN);
+  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_total = (p.k + kBlockK - 1) / kBlockK;
+  const int tiles_r = (p.rows_r + kTileR - 1) / kTileR;
+  const int tiles_c = (p.rows_c + BN - 1) / BN;
+  const long long iters = (long long)tiles_r * tiles_c * kb_total;
+  const int G = gridDim.x;
+  const long long it_begin = iters * blockIdx.x / G, it_end = iters * (blockIdx.x + 1) / G;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], E);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&map_r);
+    tma_prefetch_desc(&map_c);
+  }
+  if (warp == E + 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == E) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t n = 0;
+      for (long long it = it_begin; it < it_end; ++it, ++n) {
+        const int tile = (int)(it / kb_total), kb = (int)(it % kb_total);
+        const int tr = tile % tiles_r, tc = tile / tiles_r;
+        const int s = n % kStages;
+        if (!mbar_wait_bounded(&empty_bar[s], ((n / kStages) & 1u) ^ 1u)) {
+          raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+          break;
+        }
+        uint8_t* dst = stage_base + (size_t)s * S::kStageBytes;
+        mbar_expect_tx(&full_bar[s], S::kStageBytes);
+        tma_load_2d(dst, &map_r, &full_bar[s], kb * kBlockK, tr * kTileR);
+        tma_load_2d(dst + kTileR * kBlockK, &map_c, &full_bar[s], kb * kBlockK, tc * BN);
+      }
+    }
+  } else if (warp == E + 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = instr_desc_f8(BN);
+      uint32_t n = 0;
+      for (long long it = it_begin; it < it_end; ++it, ++n) {
+        const int s = n % kStages, b = n & 1;
+        if (!mbar_wait_bounded(&full_bar[s], (n / kStages) & 1u) ||
+            !mbar_wait_bounded(&tmem_empty[b], ((n >> 1) & 1u) ^ 1u)) {
+          raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(stage_base + (size_t)s * S::kStageBytes);
+        const uint32_t b_addr = a_addr + kTileR * kBlockK;
+        const uint64_t da = smem_desc_k128(a_addr), db = smem_desc_k128(b_addr);
+#pragma unroll
+        for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+          umma_f8(tmem_base + b * BN, da + (uint64_t)(k * kUmmaK / 16), db + (uint64_t)(k * kUmmaK / 16), idesc,
+                  k > 0 ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);  // frees the smem stage once these MMAs have read it
+        umma_commit(&tmem_full[b]);  // hands the K block's accumulator to the epilogue
+      }
+    }
+  } else {
+    // ---------------- Epilogue warps ----------------
+    const int quad = warp & 3, half = E == 8 ? warp >> 2 : 0;
+    const int row_in_tile = quad * 32 + lane;
+    const int col0 = half * kCols;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const int epi_threads = E * 32;
+    const int epi_tid = threadIdx.x;  // epilogue warps are warps 0..E-1
+    float acc[kCols];
+    uint32_t n = 0;
+    bool ok = true;
+    long long it = it_begin;
+    while (it < it_end && ok) {
+      const int tile = (int)(it / kb_total), kb_first = (int)(it % kb_total);
+      const int tr = tile % tiles_r, tc = tile / tiles_r;
+      const long long tile_it0 = (long long)tile * kb_total;
+      const long long seg_end = tile_it0 + kb_total < it_end ? tile_it0 + kb_total : it_end;
+      const int kb_last = (int)(seg_end - tile_it0);  // exclusive
+#pragma unroll
+      for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+
+      // Logical coordinates of this thread's accumulator row.
+      const int r_glob = tr * kTileR + row_in_tile;  // token (normal) or weight row (swapped)
+      const int wblk = kSwap ? tr : (tc * BN + col0) / 128;  // weight scale block of this warp's slice
+
+      for (int kb = kb_first; kb < kb_last && ok; ++kb, ++n) {
+        const int b = n & 1;
+        float s_row = 0.f;
+        if (kSwap) {
+          // svec[c] = a_scale[token c] * w_scale, shared by all epilogue threads.
+          const float ws = p.w_scale[(long long)wblk * p.w_scale_ld + kb];
+          for (int c = epi_tid; c < BN; c += epi_threads) {
+            const int tok = tc * BN + c;
+            svec[b * BN + c] = tok < p.m ? p.a_scale[(long long)kb * p.a_scale_ld + tok] * ws : 0.f;
+          }
+          epi_bar_sync(epi_threads);
+        } else {
+          const float ws = p.w_scale[(long long)wblk * p.w_scale_ld + kb];
+          s_row = r_glob < p.m ? p.a_scale[(long long)kb * p.a_scale_ld + r_glob] * ws : 0.f;
+        }
+        if (!mbar_wait_bounded(&tmem_full[b], (n >> 1) & 1u)) {
+          raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t taddr = lane_addr + (uint32_t)(b * BN + col0);
+        if constexpr (kCols % 32 == 0) {
+#pragma unroll
+          for (int c = 0; c < kCols; c += 32) {
+            float d[32];
+            tmem_ld32(taddr + c, d);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float s = kSwap ? svec[b * BN + col0 + c + j] : s_row;
+              acc[c + j] = fmaf(d[j], s, acc[c + j]);
+            }
+          }
+        } else {
+          float d[16];
+          tmem_ld16(taddr, d);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float s = kSwap ? svec[b * BN + col0 + j] : s_row;
+            acc[j] = fmaf(d[j], s, acc[j]);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[b]);
+      }
+      if (!ok) break;
+
+      // ---- segment done: direct store, or partial + last-arriver reduction ----
+      const bool whole = kb_first == 0 && kb_last == kb_total;
+      bool do_store = whole;
+      if (!whole) {
+        const int slot = it == it_begin ? 0 : 1;
+        float* ws_tile = p.workspace + ((size_t)blockIdx.x * 2 + slot) * (size_t)(BN * kTileR);
+#pragma unroll
+        for (int j = 0; j < kCols; ++j) ws_tile[(size_t)(col0 + j) * kTileR + row_in_tile] = acc[j];
+        __threadfence();
+        epi_bar_sync(epi_threads);
+        if (epi_tid == 0) {
+          // Contributors of this tile = CTAs whose ranges intersect it.
+          const long long t0 = tile_it0, t1 = tile_it0 + kb_total;
+          int c_first = (int)((t0 * G) / iters);
+          while (iters * (c_first + 1) / G <= t0) ++c_first;
+          while (c_first > 0 && iters * c_first / G > t0) --c_first;
+          int c_last = c_first;
+          while (iters * (c_last + 1) / G < t1) ++c_last;
+          const int contributors = c_last - c_first + 1;
+          const int old = atomicAdd(&p.tile_counters[tile], 1);
+          const bool last = old == contributors - 1;
+          if (last) p.tile_counters[tile] = 0;
+          last_flag[0] = last ? 1 : 0;
+          last_flag[1] = c_first;
+          last_flag[2] = c_last;
+        }
+        epi_bar_sync(epi_threads);
+        if (last_flag[0]) {
+          __threadfence();
+          const int c_first = last_flag[1], c_last = last_flag[2];
+#pragma unroll
+          for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+          for (int c = c_first; c <= c_last; ++c) {
+            const long long r0 = iters * c / G;
+            const int cslot = (r0 >= tile_it0) ? 0 : 1;  // a segment that opens its CTA's range is slot 0
+            const float* src = p.workspace + ((size_t)c * 2 + cslot) * (size_t)(BN * kTileR);
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) acc[j] += __ldcg(&src[(size_t)(col0 + j) * kTileR + row_in_tile]);
+          }
+          do_store = true;
+        }
+        epi_bar_sync(epi_threads);  // last_flag is reused by the next segment
+      }
+      if (do_store) {
+        if (kSwap) {
+          // acc[j] belongs to token tc*BN + col0 + j, weight row r_glob.
+          if (r_glob < p.n) {
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) {
+              const int tok = tc * BN + col0 + j;
+              if (tok < p.m) {
+                if (p.out_f16)
+                  reinterpret_cast<__half*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2half_rn(acc[j]);
+                else
+                  reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)tok * p.ldy + r_glob] =
+                      __float2bfloat16_rn(acc[j]);
+              }
+            }
+          }
+        } else if (r_glob < p.m) {
+          const int n0 = tc * BN + col0;
+          uint16_t* yrow = reinterpret_cast<uint16_t*>(p.y) + (long long)r_glob * p.ldy + n0;
+          const bool vec = (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) && (n0 + kCols <= p.n);
+          if (vec) {
+#pragma unroll
+            for (int j = 0; j < kCols; j += 8) {
+              uint32_t w[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                w[q] = p.out_f16 ? Mma16816<__half>::pack(acc[j + 2 * q], acc[j + 2 * q + 1])
+                                 : Mma16816<__nv_bfloat16>::pack(acc[j + 2 * q], acc[j + 2 * q + 1]);
+              }
+              *reinterpret_cast<uint4*>(yrow + j) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < kCols; ++j) {
+              if (n0 + j < p.n) {
+                if (p.out_f16)
+                  reinterpret_cast<__half*>(yrow)[j] = __float2half_rn(acc[j]);
+                else
+                  reinterpret_cast<__nv_bfloat16*>(yrow)[j] = __float2bfloat16_rn(acc[j]);
+              }
+            }
+          }
+        }
+      }
+      it = seg_end;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == E + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// --------------------------------------------------------------------------
+// Activation quantiser: per token, per 128 columns.  One half-warp per group.
+// --------------------------------------------------------------------------
+template <typename T>
+__global__ void quantize_kernel(const T* __restrict__ x, long long ldx, uint8_t* __restrict__ q, long long ldq,
+                                float* __restrict__ scales, int scale_ld, int m, int k) {
+  const int groups = (k + 127) / 128;
+  const long long hw = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 4;  // half-warp id
+  const int l16 = threadIdx.x & 15;
+  const bool live = hw < (long long)m * groups;  // dead lanes still take part in the shuffles
+  const int row = live ? (int)(hw / groups) : 0, grp = live ? (int)(hw % groups) : 0;
+  const int c0 = grp * 128 + l16 * 8;
+  float v[8];
+  const T* src = x + (long long)row * ldx + c0;
+  if (!live) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+  } else if (c0 + 8 <= k && ((reinterpret_cast<uintptr_t>(src) & 15) == 0)) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = to_float<T>(e[j]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = c0 + j < k ? to_float<T>(src[j]) : 0.f;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if (!live) return;
+  const float scale = __fdiv_rn(amax, 448.0f);  // raw scale is what gets stored (0 for a zero group)
+  const float denom = fmaxf(scale, 1e-12f);
+  uint32_t packed[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+        make_float2(__fdiv_rn(v[4 * h], denom), __fdiv_rn(v[4 * h + 1], denom)), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+        make_float2(__fdiv_rn(v[4 * h + 2], denom), __fdiv_rn(v[4 * h + 3], denom)), __NV_SATFINITE, __NV_E4M3);
+    packed[h] = (uint32_t)lo | ((uint32_t)hi << 16);
+  }
+  uint8_t* dst = q + (long long)row * ldq + c0;
+  if (c0 + 8 <= k && ((reinterpret_cast<uintptr_t>(dst) & 7) == 0)) {
+    *reinterpret_cast<uint2*>(dst) = make_uint2(packed[0], packed[1]);
+  } else {
+    const uint8_t* b = reinterpret_cast<const uint8_t*>(packed);
+    for (int j = 0; j < 8; ++j)
+      if (c0 + j < k) dst[j] = b[j];
+  }
+  if (l16 == 0) scales[(long long)grp * scale_ld + row] = scale;
+}
+
+// --------------------------------------------------------------------------
+// Host side
+// --------------------------------------------------------------------------
+struct Map2Key {
+  const void* ptr;
+  long long rows, k, ld;
+  int box_rows;
+  bool operator==(const Map2Key& o) const {
+    return ptr == o.ptr && rows == o.rows && k == o.k && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct Map2Hash {
+  size_t operator()(const Map2Key& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ (size_t)k.rows;
+    h = h * 1000003u ^ (size_t)k.k;
+    h = h * 1000003u ^ (size_t)k.ld;
+    h = h * 1000003u ^ (size_t)k.box_rows;
+    return h;
+  }
+};
+
+int operand_map(const void* ptr, long long rows, long long k, long long ld, int box_rows, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<Map2Key, CUtensorMap, Map2Hash> cache;
+  Map2Key key{ptr, rows, k, ld, box_rows};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return MIE_OK;
+    }
+  }
+  const uint64_t dims[2] = {(uint64_t)k, (uint64_t)rows};
+  const uint64_t strides[1] = {(uint64_t)ld};
+  const uint32_t box[2] = {(uint32_t)kBlockK, (uint32_t)box_rows};
+  const int rc = make_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MIE_OK) return rc;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 16384) cache.clear();
+  cache.emplace(key, *out);
+  return MIE_OK;
+}
+
+template <int BN, int E, bool kSwap>
+int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& p, int grid, cudaStream_t stream) {
+  using S = GemmSmem<BN, E>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  MIE_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    MIE_CUDA(cudaFuncSetAttribute(fp8_gemm_kernel<BN, E, kSwap>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  S::kTotal));
+    configured[dev] = true;
+  }
+  fp8_gemm_kernel<BN, E, kSwap><<<grid, (E + 2) * 32, S::kTotal, stream>>>(mr, mc, p);
+  MIE_LAUNCH_CHECK("fp8_gemm_kernel");
+  return MIE_OK;
+}
+
+// Column-tile width for the swapped orientation: smallest of 16/32/64/128 covering m.
+int swap_bn(int m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
+
+}  // namespace
+}  // namespace mie
+
+using namespace mie;
+
+extern "C" int64_t mie_fp8_gemm_workspace_bytes(int32_t m, int32_t n, int32_t k) {
+  (void)n;
+  (void)k;
+  const int bn = m <= 128 ? swap_bn(m) : 256;
+  // One int32 counter per tile (a fixed block of 65536) followed by two fp32 partial tiles per CTA.
+  return (long long)kCounterInts * 4 + (long long)sm_count() * 2 * bn * kTileR * 4;
+}
+
+extern "C" int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t ldq, float* scales,
+                                int32_t scale_ld, int32_t m, int32_t k, void* stream) {
+  MIE_CHECK_ARG(x && q && scales, "null pointer");
+  MIE_CHECK_ARG(dtype == MIE_DTYPE_BF16 || dtype == MIE_DTYPE_F16, "activation must be bf16 or fp16");
+  MIE_CHECK_ARG(m >= 0 && k >= 1 && scale_ld >= m && ldx >= k && ldq >= k, "invalid quantiser shape");
+  if (m == 0) return MIE_OK;
+  const long long half_warps = (long long)m * ((k + 127) / 128);
+  const int threads = 256;
+  const long long blocks = (half_warps * 16 + threads - 1) / threads;
+  if (dtype == MIE_DTYPE_BF16)
+    quantize_kernel<__nv_bfloat16><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, ldx, (uint8_t*)q, ldq, scales, scale_ld, m, k);
+  else
+    quantize_kernel<__half><<<(unsigned)blocks, threads, 0, (cudaStream_t)stream>>>(
+        (const __half*)x, ldx, (uint8_t*)q, ldq, scales, scale_ld, m, k);
+  MIE_LAUNCH_CHECK("quantize_kernel");
+  return MIE_OK;
+}
+
+extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
+                            int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy,
+                            int32_t out_dtype, int32_t m, int32_t n, int32_t k, void* workspace,
+                            int64_t workspace_bytes, int32_t* status, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MIE_CHECK_ARG(x8 && a_scale && w8 && w_scale && y && workspace, "null pointer");
+  MIE_CHECK_ARG(m >= 0 && n >= 1 && k >= 1, "invalid GEMM shape %d x %d x %d", m, n, k);
+  MIE_CHECK_ARG(out_dtype == MIE_DTYPE_BF16 || out_dtype == MIE_DTYPE_F16, "output must be bf16 or fp16");
+  MIE_CHECK_ARG(ldx % 16 == 0 && ldw % 16 == 0, "operand row strides must be multiples of 16 bytes");
+  MIE_CHECK_ARG(((reinterpret_cast<uintptr_t>(x8) | reinterpret_cast<uintptr_t>(w8)) & 15) == 0,
+                "operands must be 16-byte aligned");
+  MIE_CHECK_ARG(ldy >= n && a_scale_ld >= m && w_scale_ld >= (k + 127) / 128, "invalid leading dimension");
+  if (m == 0) return MIE_OK;
+
+  const bool swap = m <= 128;
+  const int bn = swap ? swap_bn(m) : 256;
+  const int kb = (k + kBlockK - 1) / kBlockK;
+  const long long tiles_r = swap ? (n + kTileR - 1) / kTileR : (m + kTileR - 1) / kTileR;
+  const long long tiles_c = swap ? (m + bn - 1) / bn : (n + bn - 1) / bn;
+  const long long tiles = tiles_r * tiles_c;
+  const long long iters = tiles * kb;
+  const int sms = sm_count();
+  const int grid = (int)(iters < sms ? iters : sms);
+  const long long need = (long long)kCounterInts * 4 + (long long)grid * 2 * bn * kTileR * 4;
+  MIE_CHECK_ARG(tiles <= kCounterInts, "too many output tiles (%lld)", tiles);
+  MIE_CHECK_ARG(workspace_bytes >= need, "workspace of %lld bytes is too small (need %lld)",
+                (long long)workspace_bytes, need);
+  MIE_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+
+  GemmParams p;
+  p.rows_r = swap ? n : m;
+  p.rows_c = swap ? m : n;
+  p.k = k;
+  p.m = m;
+  p.n = n;
+  p.a_scale = a_scale;
+  p.a_scale_ld = a_scale_ld;
+  p.w_scale = w_scale;
+  p.w_scale_ld = w_scale_ld;
+  p.y = y;
+  p.ldy = ldy;
+  p.out_f16 = out_dtype == MIE_DTYPE_F16;
+  // Counters sit at the front so their position does not depend on the shape;
+  // they must be zero before the first launch and are left zero by every launch.
+  p.tile_counters = reinterpret_cast<int*>(workspace);
+  p.workspace = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + (size_t)kCounterInts * 4);
+  p.status = status;
+
+  CUtensorMap mr, mc;
+  if (swap) {
+    if (int rc = operand_map(w8, n, k, ldw, kTileR, &mr)) return rc;
+    if (int rc = operand_map(x8, m, k, ldx, bn, &mc)) return rc;
+    switch (bn) {
+      case 16: return launch_gemm<16, 4, true>(mr, mc, p, grid, stream);
+      case 32: return launch_gemm<32, 4, true>(mr, mc, p, grid, stream);
+      case 64: return launch_gemm<64, 4, true>(mr, mc, p, grid, stream);
+      default: return launch_gemm<128, 4, true>(mr, mc, p, grid, stream);
+    }
+  }
+  if (int rc = operand_map(x8, m, k, ldx, kTileR, &mr)) return rc;
+  if (int rc = operand_map(w8, n, k, ldw, bn, &mc)) return rc;
+  return launch_gemm<256, 8, false>(mr, mc, p, grid, stream);
+}
