@@ -1,0 +1,404 @@
+"""Benchmark of the continuous-batching decode hot path on B200.
+
+Metric (BASELINE.json): decode tok/s of a random-init Qwen3-4B-shaped FP8 model on a
+ragged batch, with the paged-attention HBM GB/s as a fraction of peak.
+
+Workload (BASELINE configuration 4): C concurrent sequences (default 256) whose
+contexts are log-normal (median 2048, sigma 1.0, clipped to [16, 32768]), random
+block tables over a KV pool of about 80% of free HBM, split-KV decode attention,
+one CUDA-graph decode step per "step"; tensor-parallel over --gpus ranks.
+
+    python bench.py --gpus 1 --steps 200 --warmup 3
+    python -m torch.distributed.run --nproc-per-node 8 ... bench.py --gpus 8 ...
+    python bench.py --impl reference        # the reference's torch/CPU path on host cores
+
+Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+FALLBACK_HBM_GBS = 6650.0
+METRIC = "decode tok/s (Qwen3-4B FP8 shape, ragged batch); paged-attn HBM GB/s % peak"
+
+
+def parse_args() -> argparse.Namespace:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=3)
+    parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    parser.add_argument("--concurrency", type=int, default=256)
+    parser.add_argument("--kv-fraction", type=float, default=0.8)
+    parser.add_argument("--layers", type=int, default=None, help="debug: fewer layers (invalid as a result)")
+    parser.add_argument("--no-cpu-baseline", action="store_true")
+    parser.add_argument("--no-e2e", action="store_true")
+    return parser.parse_args()
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        try:
+            return float(json.loads(path.read_text())["hbm_gbs"]), "measured"
+        except (ValueError, KeyError):
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+# ----------------------------------------------------------------------------------------------
+# Clock sampling during the timed region
+# ----------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int) -> None:
+        self.device_index, self.process, self.path = device_index, None, None
+
+    def start(self) -> None:
+        try:
+            import tempfile
+
+            handle = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = handle.name
+            self.process = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device_index)], stdout=handle, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.process = None
+
+    def stop(self) -> dict:
+        if self.process is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        clocks, max_clock, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        try:
+            for line in Path(self.path).read_text().splitlines():
+                fields = [f.strip() for f in line.split(",")]
+                if len(fields) < 9:
+                    continue
+                try:
+                    clocks.append(float(fields[1]))
+                    max_clock = float(fields[2])
+                except ValueError:
+                    continue
+                for name, value in zip(names, fields[5:9]):
+                    if value.lower().startswith("active"):
+                        reasons.add(name)
+            os.unlink(self.path)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU baseline: the reference's torch/CPU path (oracle port) on a bounded sample
+# ----------------------------------------------------------------------------------------------
+
+def cpu_decode_baseline(sample_sequences: int = 4, max_context: int = 4096, repeats: int = 1,
+                        layer_source=None, embedding=None, final_norm=None) -> dict:
+    """Time one decode step of ONE layer (+ the tied lm_head) of the Qwen3-4B-shaped FP8 model on the host
+    cores with the CPU oracle, and extrapolate to the 36-layer model: tok/s = S / (36 * t_layer + t_head)."""
+
+    from mini_inference_engine_b200 import workloads
+    from mini_inference_engine_b200.engine.model_runner.qwen3_decode import Qwen3Shape, Qwen3Weights
+    from oracle import hot_path, qwen3_model
+
+    shape = Qwen3Shape()
+    threads = torch.get_num_threads()
+    contexts = workloads.lognormal_contexts(256, seed=256)[:sample_sequences].clamp(max=max_context)
+    if layer_source is None:
+        weights = Qwen3Weights(shape, torch.device("cpu"), seed=0, layers=1)
+    else:
+        class _W:  # one layer copied from the device model
+            pass
+        weights = _W()
+        weights.layers = [type(layer_source)(*[getattr(layer_source, f).cpu()
+                                                for f in layer_source.__dataclass_fields__])]
+        weights.embedding, weights.final_norm = embedding.cpu(), final_norm.cpu()
+    pages = int(sum(-(-(int(n) + 2) // 16) for n in contexts)) + 4
+    tables = workloads.random_block_tables(contexts, num_pages=pages, seed=3, extra_tokens=2)
+    key_blocks = torch.randn(1, pages, shape.kv_heads, 16, shape.head_dim).to(torch.bfloat16)
+    value_blocks = torch.randn(1, pages, shape.kv_heads, 16, shape.head_dim).to(torch.bfloat16)
+    ids = torch.randint(0, shape.vocab, (sample_sequences,))
+    lengths = (contexts + 1).to(torch.int32)
+
+    def one_layer_step():
+        # decode_step over a 1-layer model = one layer + final norm + lm_head + argmax.
+        return qwen3_model.decode_step(weights, key_blocks, value_blocks, ids, lengths, tables,
+                                       q_heads=shape.q_heads, kv_heads=shape.kv_heads, head_dim=shape.head_dim,
+                                       eps=shape.rms_eps, theta=shape.rope_theta)
+
+    def head_only():
+        final = hot_path.rms_norm(weights.embedding[:sample_sequences], weights.final_norm, shape.rms_eps)
+        return (final @ weights.embedding.t()).argmax(dim=-1)
+
+    one_layer_step()
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        one_layer_step()
+    t_step = (time.perf_counter() - t0) / repeats
+    t0 = time.perf_counter()
+    head_only()
+    t_head = time.perf_counter() - t0
+    t_layer = max(t_step - t_head, 1e-6)
+    full = shape.layers * t_layer + t_head
+    return {
+        "value": sample_sequences / full, "unit": "tok/s", "cores": threads, "kind": "port",
+        "sample": (f"{sample_sequences} sequences (contexts {contexts.tolist()}), one decode step of 1 layer + "
+                   f"lm_head timed with the CPU oracle ({t_layer * 1e3:.0f} ms/layer, {t_head * 1e3:.0f} ms head), "
+                   f"extrapolated to 36 layers"),
+        "seconds_per_step_extrapolated": full,
+    }
+
+
+def run_reference_arm(args: argparse.Namespace) -> None:
+    """The reference's own CPU path for this metric: its torch block-wise attention and the FP8 linear
+    restated on the CPU (the reference has no CPU FP8 kernel), on all host threads."""
+
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    repeats = max(1, min(args.steps, 2))
+    started = time.perf_counter()
+    base = cpu_decode_baseline(repeats=repeats)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["seconds_per_step_extrapolated"] * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3/bf16",
+        "data": "synthetic",
+        "config": {"workload": "config4 ragged decode, CPU sample", "sample": base["sample"],
+                   "timed_repeats": repeats},
+        "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "wall_seconds": time.perf_counter() - started,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------
+# Our arm
+# ----------------------------------------------------------------------------------------------
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    from mini_inference_engine_b200 import workloads
+    from mini_inference_engine_b200.engine.kv_cache.triton_paged_attention import launch_decode_attention
+    from mini_inference_engine_b200.engine.model_runner.qwen3_decode import (
+        Qwen3DecodeRunner,
+        Qwen3Shape,
+        Qwen3Weights,
+    )
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=device)
+        group = torch.distributed.group.WORLD
+    tp = world
+
+    def barrier() -> None:
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+
+    def max_over_ranks(value: float) -> float:
+        if world == 1:
+            return value
+        t = torch.tensor([value], dtype=torch.float64, device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        return float(t.item())
+
+    shape = Qwen3Shape()
+    concurrency, steps, warmup = args.concurrency, args.steps, max(args.warmup, 0)
+    weights = Qwen3Weights(shape, device, seed=0, tp_rank=rank, tp_size=tp, layers=args.layers)
+    layers = len(weights.layers)
+    contexts = workloads.lognormal_contexts(concurrency, seed=concurrency)
+    e2e_steps = 0 if args.no_e2e else steps
+    planned_steps = 2 * (warmup + steps) + 16
+    max_context = int(contexts.max()) + planned_steps + 1
+    local_kv = shape.kv_heads // tp
+    page_bytes = layers * 2 * local_kv * shape.page * shape.head_dim * 2
+    needed_pages = int(sum(-(-(int(n) + planned_steps + 1) // shape.page) for n in contexts)) + 8
+    torch.cuda.synchronize(device)
+    free_bytes, _ = torch.cuda.mem_get_info(device)
+    # Leave room for logits, graph pools and scratch.
+    pool_pages = int(max(free_bytes - (6 << 30), 0) * args.kv_fraction) // page_bytes
+    if world > 1:
+        t = torch.tensor([pool_pages], dtype=torch.int64, device=device)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
+        pool_pages = int(t.item())
+    num_pages = max(pool_pages, needed_pages)
+    runner = Qwen3DecodeRunner(weights, num_pages=num_pages, max_batch=concurrency, max_context=max_context,
+                               process_group=group, kv_init="normal")
+    tables = workloads.random_block_tables(contexts, num_pages=num_pages, page=shape.page, seed=concurrency,
+                                           extra_tokens=planned_steps + 1)
+    width = tables.shape[1]
+    ids0 = torch.randint(0, shape.vocab, (concurrency,), generator=torch.Generator().manual_seed(1))
+
+    # ---- device-resident measurement: the graph feeds its tokens back and bumps the lengths ----
+    buffers = runner.capture(concurrency, width, advance=True)
+    launches_per_step = runner.launches_per_step
+    buffers.input_ids.copy_(ids0.to(device))
+    buffers.block_tables.copy_(tables.to(device))
+    buffers.sequence_lengths.copy_((contexts + 1).to(torch.int32).to(device))
+    for _ in range(warmup):
+        runner.replay(concurrency)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        runner.replay(concurrency)
+    end.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else {}
+    elapsed_ms = max_over_ranks(start.elapsed_time(end))
+    runner.check_status()
+    tokens_per_s = concurrency * steps / (elapsed_ms / 1e3)
+    grown = warmup + steps  # tokens every context has gained so far
+
+    # ---- end to end: host metadata in, H2D, replay, D2H of the sampled tokens, every step ----
+    e2e = None
+    if e2e_steps:
+        runner.capture(concurrency, width, advance=False)
+        host_lengths = (contexts + 1 + grown).to(torch.int32)
+        host_ids = buffers.output_tokens.cpu()
+        for _ in range(warmup):
+            host_ids, _, _ = runner.step_host(concurrency, host_ids, host_lengths, tables)
+            host_ids = host_ids.clone()
+            host_lengths += 1
+        barrier()
+        h2d = d2h = 0
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            host_ids, h2d, d2h = runner.step_host(concurrency, host_ids, host_lengths, tables)
+            host_ids = host_ids.clone()
+            host_lengths += 1
+        torch.cuda.synchronize(device)
+        wall = max_over_ranks(time.perf_counter() - t0)
+        barrier()
+        runner.check_status()
+        e2e = {"value": concurrency * e2e_steps / wall, "unit": "tok/s", "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": wall / e2e_steps * 1e3}
+        grown += warmup + e2e_steps
+
+    # ---- roofline of the dominant kernel: paged decode attention, timed alone with CUDA events ----
+    lengths_now = (contexts + 1 + grown).to(torch.int32).to(device)
+    tables_dev = buffers.block_tables
+    lq = shape.q_heads // tp
+    query = torch.randn(concurrency, lq, 1, shape.head_dim, device=device).to(torch.bfloat16)
+    out = torch.empty_like(query)
+    launch_decode_attention(query, out, runner.key_blocks[0], runner.value_blocks[0], tables_dev, lengths_now, None,
+                            scale=shape.head_dim ** -0.5, max_total_tokens=concurrency * max_context,
+                            scratch=runner.scratch, split_policy=1, plan_only=True, status=runner.status)
+    durations = []
+    for rep in range(3):
+        for layer in range(layers):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            launch_decode_attention(query, out, runner.key_blocks[layer], runner.value_blocks[layer], tables_dev,
+                                    lengths_now, None, scale=shape.head_dim ** -0.5,
+                                    max_total_tokens=concurrency * max_context, scratch=runner.scratch,
+                                    split_policy=1, use_plan=True, plan_slot=layer,
+                                    status=runner.status)
+            e1.record()
+            if rep > 0:
+                durations.append((e0, e1))
+            if layer == layers - 1:
+                # Work counters are consumed by a launch: rebuild the plan before the next sweep.
+                launch_decode_attention(query, out, runner.key_blocks[0], runner.value_blocks[0], tables_dev,
+                                        lengths_now, None, scale=shape.head_dim ** -0.5,
+                                        max_total_tokens=concurrency * max_context, scratch=runner.scratch,
+                                        split_policy=1, plan_only=True, status=runner.status)
+    torch.cuda.synchronize(device)
+    attn_ms = statistics.mean(a.elapsed_time(b) for a, b in durations)
+    total_tokens = int(lengths_now.sum().item())
+    kv_bytes_per_token = 2 * (shape.kv_heads // tp) * shape.head_dim * 2
+    algorithmic = total_tokens * kv_bytes_per_token + 2 * concurrency * lq * shape.head_dim * 2
+    peak, peak_kind = measured_peaks()
+    achieved = algorithmic / (attn_ms / 1e3) / 1e9
+    traffic = None
+    ratio_file = ROOT / "profiles" / "decode_attention_dram_ratio.json"
+    if ratio_file.exists():
+        try:
+            traffic = algorithmic * float(json.loads(ratio_file.read_text())["dram_bytes_per_algorithmic_byte"])
+        except (ValueError, KeyError):
+            traffic = None
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                "traffic": traffic, "peak_kind": peak_kind, "kernel": "decode_kernel<bf16> + merge_kernel",
+                "algorithmic_bytes_per_launch": algorithmic, "ms_per_launch": attn_ms}
+    runner.check_status()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            cpu_all = cpu_decode_baseline(layer_source=weights.layers[0], embedding=weights.embedding,
+                                          final_norm=weights.final_norm)
+            cpu = {k: cpu_all[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        except Exception as error:  # the baseline is reported, never required
+            cpu = {"value": None, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
+                   "sample": f"failed: {error!r}"}
+
+    if rank == 0:
+        step_bytes = weights.weight_bytes() + total_tokens * kv_bytes_per_token * layers
+        line = {
+            "metric": METRIC, "value": tokens_per_s, "unit": "tok/s", "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": elapsed_ms / steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "fp8_e4m3 GEMM / bf16 KV+activations", "data": "synthetic",
+            "config": {
+                "workload": "config4: ragged decode sweep point", "concurrency": concurrency,
+                "context": "lognormal(median 2048, sigma 1.0) clipped [16, 32768]",
+                "total_context_tokens": total_tokens, "layers": layers, "parallelism": f"tp{tp}",
+                "kv_pool_pages": num_pages, "kv_pool_gb_per_gpu": num_pages * page_bytes / 1e9,
+                "split_kv": "length-proportional chunks chosen on the device",
+                "l2": "inputs larger than L2 (KV pool and weights are re-read from HBM every step)",
+                "graph": "one CUDA graph per decode step",
+            },
+            "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
+            "gpu_launches": launches_per_step * steps, "clocks": clocks,
+            "step_hbm_bytes_per_gpu": step_bytes,
+            "step_hbm_frac_of_peak": step_bytes / (elapsed_ms / steps / 1e3) / 1e9 / peak,
+        }
+        if args.layers is not None:
+            line["invalid"] = "debug run with fewer layers"
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -169,6 +169,27 @@ int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mie_view4_t k
                                int32_t use_plan, int32_t plan_slot, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------
+ * Chunked-prefill attention
+ * ---------------------------------------------------------------------- */
+
+/*
+ * Replaces triton_flash_prefill_attention (engine/kv_cache/triton_flash_prefill.py:154-202,
+ * kernel :58-151) and, through the Python shim, triton_packed_prefill_attention
+ * (engine/kv_cache/triton_packed_attention.py:186-259): packed varlen causal
+ * attention over K/V pages that already contain the new tokens.  query / out
+ * [tokens, q_heads, head_dim] (token and head strides in elements, head_dim
+ * contiguous); request r owns rows cu_seqlens[r] .. cu_seqlens[r+1] and sees
+ * kv_lens[r] keys, query row i at position kv_lens[r] - q_len + i.
+ * max_query_len is a host bound that sizes the grid.  head_dim 128, bf16/fp16.
+ */
+int mie_flash_prefill_attention(const void* query, int64_t q_token_stride, int64_t q_head_stride, void* out,
+                                int64_t o_token_stride, int64_t o_head_stride, mie_view4_t key_blocks,
+                                mie_view4_t value_blocks, mie_index_t block_tables, mie_index_t cu_seqlens,
+                                mie_index_t kv_lens, int32_t requests, int32_t max_query_len, int32_t q_heads,
+                                int32_t kv_heads, int32_t head_dim, int32_t block_size, int32_t num_blocks,
+                                int32_t table_width, int32_t dtype, float scale, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------
  * FP8 128x128 block-scaled linear
  * ---------------------------------------------------------------------- */
 
@@ -183,8 +204,8 @@ int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mie_view4_t k
 int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t ldq, float* scales,
                      int32_t scale_ld, int32_t m, int32_t k, void* stream);
 
-/* Bytes of workspace mie_fp8_gemm needs.  The first 262144 bytes (tile counters)
- * must be zero before the first launch; every launch leaves them zero. */
+/* Bytes of workspace (fp32 partial tiles of the stream-K schedule) mie_fp8_gemm needs;
+ * the contents need not be initialised. */
 int64_t mie_fp8_gemm_workspace_bytes(int32_t m, int32_t n, int32_t k);
 
 /*
@@ -195,11 +216,76 @@ int64_t mie_fp8_gemm_workspace_bytes(int32_t m, int32_t n, int32_t k);
  * x8 [m, k] e4m3 (row stride ldx bytes), a_scale as mie_fp8_quantize writes it,
  * w8 [n, k] e4m3 (row stride ldw bytes), w_scale [ceil(n/128), w_scale_ld].
  * Operand base pointers and row strides must be multiples of 16 bytes.
+ * grid_limit > 0 caps the number of persistent CTAs (0: one per SM).  trace is a
+ * profiling aid: NULL, or a device buffer of 16 int64 per CTA that receives
+ * %globaltimer stamps of the kernel's phases.
  */
 int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
                  int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy, int32_t out_dtype,
-                 int32_t m, int32_t n, int32_t k, void* workspace, int64_t workspace_bytes, int32_t* status,
+                 int32_t m, int32_t n, int32_t k, void* workspace, int64_t workspace_bytes, int32_t grid_limit,
+                 int32_t* status, int64_t* trace, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Fused memory-bound glue (bf16 activations)
+ * ---------------------------------------------------------------------- */
+
+/*
+ * Replaces rms_norm (engine/kernels/fused.py:165-203, kernel :90-124) for
+ * contiguous rows: out = weight * bf16(x * rsqrt(mean(x^2) + eps)) with fp32
+ * math.  With `residual` the row normalised is bf16(x + residual), which is
+ * also stored to `summed` (the reference's (normed, summed) pair).  When `q`
+ * is given the normalised row is additionally quantised for the next FP8 GEMM
+ * (e4m3 + per-128 scales in mie_fp8_quantize's layout; cols % 128 == 0) and
+ * `out` may be NULL.  cols % 8 == 0, cols <= 8192.
+ */
+int mie_rms_norm(const void* x, int64_t ldx, const void* residual, void* summed, const void* weight, void* out,
+                 void* q, int64_t ldq, float* scales, int32_t scale_ld, int32_t rows, int32_t cols, float eps,
                  void* stream);
+
+/*
+ * Replaces rms_norm on per-head strided rows (engine/kernels/fused.py:178-189:
+ * q/k norm over column views of the merged qkv output).  Row r = (r / heads,
+ * r % heads) starts at x + (r / heads) * outer_stride + (r % heads) *
+ * head_stride; width is 128; out is contiguous [rows_total, 128].
+ */
+int mie_head_rms_norm(const void* x, int64_t outer_stride, int64_t head_stride, int32_t heads, const void* weight,
+                      void* out, int64_t rows_total, float eps, void* stream);
+
+/*
+ * Replaces silu_mul (engine/kernels/fused.py:217-233, kernel :127-137):
+ * out = bf16(bf16(silu(gate)) * up); gate/up rows share the stride ld_in (column
+ * views of the merged gate_up output); out is contiguous.  Optional fused
+ * quantisation as in mie_rms_norm.
+ */
+int mie_silu_mul(const void* gate, const void* up, int64_t ld_in, void* out, void* q, int64_t ldq, float* scales,
+                 int32_t scale_ld, int32_t rows, int32_t cols, void* stream);
+
+/*
+ * Replaces _rope_kernel / apply_rotary_pos_emb (engine/kernels/fused.py:140-162,
+ * :247-262): rotate-half RoPE on x [batch, heads, seq, dim] with cos/sin
+ * [batch or 1, seq, dim] (cs_batch_stride 0 broadcasts), each product rounded
+ * to bf16 before the add.
+ */
+int mie_rope(mie_view4_t x, const void* cos, const void* sin, int64_t cs_batch_stride, int64_t cs_token_stride,
+             mie_view4_t out, int32_t batch, int32_t heads, int32_t seq, int32_t dim, void* stream);
+
+/*
+ * One pass over a merged qkv GEMM output [tokens, (q_heads + 2 kv_heads) * 128]
+ * that replaces, for the flat-token paths of PagedQwen3Attention
+ * (engine/kv_cache/qwen3_paged.py:191-219 and :244-288): q_norm / k_norm
+ * (per-head RMSNorm), apply_rotary_pos_emb, and the KV-cache write
+ * (triton_write_decode_kv / triton_write_packed_kv).  cos_sin is a table
+ * [max_pos][2][128] (cos row, sin row) indexed by positions[t]; K and V rows go
+ * to page block_tables[seq][pos / block_size], slot pos % block_size with seq =
+ * token_to_sequence[t] (or t when that pointer is NULL); the normalised, rotated
+ * queries go to q_out [tokens, q_heads, 128].
+ */
+int mie_qkv_norm_rope_write(const void* qkv, int64_t ld, const void* q_weight, const void* k_weight,
+                            const void* cos_sin, int32_t max_pos, mie_index_t positions,
+                            mie_index_t token_to_sequence, mie_index_t block_tables, void* q_out,
+                            mie_view4_t key_blocks, mie_view4_t value_blocks, int32_t tokens, int32_t q_heads,
+                            int32_t kv_heads, int32_t block_size, int32_t num_blocks, int32_t table_rows,
+                            int32_t table_width, float eps, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -65,12 +65,27 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                                   c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                                   c_float, c_int32, c_int64, c_void_p, c_int64, c_int32, c_int32,
                                                   c_int32, c_void_p, c_void_p]),
+    "mie_flash_prefill_attention": (ctypes.c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, View4T,
+                                                   View4T, IndexT, IndexT, IndexT, c_int32, c_int32, c_int32,
+                                                   c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_float,
+                                                   c_void_p, c_void_p]),
     "mie_fp8_quantize": (ctypes.c_int, [c_void_p, c_int64, c_int32, c_void_p, c_int64, c_void_p, c_int32, c_int32,
                                         c_int32, c_void_p]),
     "mie_fp8_gemm_workspace_bytes": (c_int64, [c_int32, c_int32, c_int32]),
     "mie_fp8_gemm": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_int32,
                                     c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_int64,
-                                    c_void_p, c_void_p]),
+                                    c_int32, c_void_p, c_void_p, c_void_p]),
+    "mie_rms_norm": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                    c_void_p, c_int32, c_int32, c_int32, c_float, c_void_p]),
+    "mie_head_rms_norm": (ctypes.c_int, [c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p, c_int64, c_float,
+                                         c_void_p]),
+    "mie_silu_mul": (ctypes.c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64, c_void_p, c_int32,
+                                    c_int32, c_int32, c_void_p]),
+    "mie_rope": (ctypes.c_int, [View4T, c_void_p, c_void_p, c_int64, c_int64, View4T, c_int32, c_int32, c_int32,
+                                c_int32, c_void_p]),
+    "mie_qkv_norm_rope_write": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, IndexT,
+                                               IndexT, IndexT, c_void_p, View4T, View4T, c_int32, c_int32, c_int32,
+                                               c_int32, c_int32, c_int32, c_int32, c_float, c_void_p, c_void_p]),
 }
 
 _lib: ctypes.CDLL | None = None

@@ -56,6 +56,11 @@ struct Scratch {
   int cap;
 };
 
+template <typename T>
+__device__ __forceinline__ float round_act(float v) {
+  return to_float<T>(from_float<T>(v));
+}
+
 __host__ __device__ inline long long align_up(long long v, long long a) { return (v + a - 1) / a * a; }
 
 // Attention read length of request b, or 0 (with a status bit) when the
@@ -203,6 +208,7 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   int* counter = p.sc.header + kCounterBase + p.counter_slot;
   const long long capacity_tokens = (long long)p.table_width * p.block_size;
   uint32_t parity = 0;
+  const uint64_t stream_policy = l2_evict_first_policy();  // K/V pages are read once per step
 
   // ldmatrix lane geometry (constant per lane).
   const int k_tok = (lane & 7) + ((lane >> 4) & 1) * 8, k_sel = (lane >> 3) & 1;
@@ -263,10 +269,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
         const int tok_in_page = (int)(tok % p.block_size);
         uint8_t* dst = stages + (size_t)s * kStageBytes;
         mbar_expect_tx(&bars[s], kStageBytes);
-        tma_load_4d(dst, &kmap, &bars[s], 0, tok_in_page, h, pids[i]);
-        tma_load_4d(dst + kTileBytes / 2, &kmap, &bars[s], 64, tok_in_page, h, pids[i]);
-        tma_load_4d(dst + kTileBytes, &vmap, &bars[s], 0, tok_in_page, h, pids[i]);
-        tma_load_4d(dst + kTileBytes + kTileBytes / 2, &vmap, &bars[s], 64, tok_in_page, h, pids[i]);
+        tma_load_4d_hint(dst, &kmap, &bars[s], 0, tok_in_page, h, pids[i], stream_policy);
+        tma_load_4d_hint(dst + kTileBytes / 2, &kmap, &bars[s], 64, tok_in_page, h, pids[i], stream_policy);
+        tma_load_4d_hint(dst + kTileBytes, &vmap, &bars[s], 0, tok_in_page, h, pids[i], stream_policy);
+        tma_load_4d_hint(dst + kTileBytes + kTileBytes / 2, &vmap, &bars[s], 64, tok_in_page, h, pids[i],
+                         stream_policy);
       };
       if (lane == 0) {
         for (int i = 0; i < kStages && i < nb; ++i) issue(i);
@@ -317,12 +324,14 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
             Mma16816<T>::run(sa[1], qa[ks][0], 0u, qa[ks][1], 0u, r2, r3);
           }
         }
-        // This lane's four scores of head g: tokens 2t, 2t+1, 8+2t, 9+2t.
+        // This lane's four scores of head g: tokens 2t, 2t+1, 8+2t, 9+2t.  The reference keeps the
+        // Q.K^T product in the activation dtype (a bf16/fp16 bmm per page) before the fp32 softmax;
+        // rounding the fp32 dot product once reproduces that.
         float sv[4];
-        sv[0] = (sa[0][0] + sb[0][0]) * p.scale_log2;
-        sv[1] = (sa[0][1] + sb[0][1]) * p.scale_log2;
-        sv[2] = (sa[1][0] + sb[1][0]) * p.scale_log2;
-        sv[3] = (sa[1][1] + sb[1][1]) * p.scale_log2;
+        sv[0] = round_act<T>(sa[0][0] + sb[0][0]) * p.scale_log2;
+        sv[1] = round_act<T>(sa[0][1] + sb[0][1]) * p.scale_log2;
+        sv[2] = round_act<T>(sa[1][0] + sb[1][0]) * p.scale_log2;
+        sv[3] = round_act<T>(sa[1][1] + sb[1][1]) * p.scale_log2;
         const int tk = 2 * t;
         if (tk >= valid) sv[0] = -INFINITY;
         if (tk + 1 >= valid) sv[1] = -INFINITY;
@@ -337,7 +346,11 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
         const float p2 = exp2f(sv[2] - m_new), p3 = exp2f(sv[3] - m_new);
         l = l * alpha + ((p0 + p1) + (p2 + p3));
         m = m_new;
+        // P.V runs on the tensor cores in the activation dtype; the reference multiplies fp32 weights by
+        // fp32 V, so P is split into a rounded part and its remainder (two MMAs) to keep ~16 more bits.
         const uint32_t pa0 = Mma16816<T>::pack(p0, p1), pa2 = Mma16816<T>::pack(p2, p3);
+        const uint32_t pb0 = Mma16816<T>::pack(p0 - round_act<T>(p0), p1 - round_act<T>(p1));
+        const uint32_t pb2 = Mma16816<T>::pack(p2 - round_act<T>(p2), p3 - round_act<T>(p3));
 #pragma unroll
         for (int n = 0; n < 16; ++n) {
           o[n][0] *= alpha;
@@ -352,6 +365,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
           ldmatrix_x4_trans(r0, r1, r2, r3, addr);
           Mma16816<T>::run(o[2 * np], pa0, 0u, pa2, 0u, r0, r1);
           Mma16816<T>::run(o[2 * np + 1], pa0, 0u, pa2, 0u, r2, r3);
+          Mma16816<T>::run(o[2 * np], pb0, 0u, pb2, 0u, r0, r1);
+          Mma16816<T>::run(o[2 * np + 1], pb0, 0u, pb2, 0u, r2, r3);
         }
         __syncwarp();
         if (lane == 0 && i + kStages < nb) issue(i + kStages);
@@ -391,26 +406,48 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
 }
 
 // Merge the chunks of split requests; also zero-fills rows with nothing to read.
+// One block per (request, query head); threads first find the global maximum and the
+// per-chunk weights together, then each thread owns one output dimension.
 template <typename T>
 __global__ void __launch_bounds__(kHeadDim) merge_kernel(DecodeParams p) {
+  constexpr int kMaxStaged = 512;
+  __shared__ float weight_s[kMaxStaged];
+  __shared__ float red[4];
   const int b = blockIdx.x / p.q_heads, head = blockIdx.x % p.q_heads;
   const int first = p.sc.offsets[b], n = p.sc.offsets[b + 1] - first;
   if (n == 1) return;
-  const int d = threadIdx.x;
+  const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
   T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)b * p.out.s[0] + (long long)head * p.out.s[1];
   if (n == 0) {
     orow[d] = from_float<T>(0.f);
     return;
   }
+  const float* pm = p.sc.part_m + (long long)first * p.q_heads + head;
+  const float* pl = p.sc.part_l + (long long)first * p.q_heads + head;
   float mmax = -INFINITY;
-  for (int i = 0; i < n; ++i) mmax = fmaxf(mmax, p.sc.part_m[(long long)(first + i) * p.q_heads + head]);
-  float acc = 0.f, lsum = 0.f;
-  for (int i = 0; i < n; ++i) {
-    const long long row = (long long)(first + i) * p.q_heads + head;
-    const float w = exp2f(p.sc.part_m[row] - mmax);
-    lsum += p.sc.part_l[row] * w;
-    acc += p.sc.part_o[row * kHeadDim + d] * w;
+  for (int i = d; i < n; i += kHeadDim) mmax = fmaxf(mmax, pm[(long long)i * p.q_heads]);
+  mmax = warp_max(mmax);
+  if (lane == 0) red[warp] = mmax;
+  __syncthreads();
+  mmax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+  __syncthreads();
+  float lsum = 0.f;
+  for (int i = d; i < n; i += kHeadDim) {
+    const float w = exp2f(pm[(long long)i * p.q_heads] - mmax);
+    if (i < kMaxStaged) weight_s[i] = w;
+    lsum += pl[(long long)i * p.q_heads] * w;
   }
+  lsum = warp_sum(lsum);
+  if (lane == 0) red[warp] = lsum;
+  __syncthreads();
+  lsum = (red[0] + red[1]) + (red[2] + red[3]);
+  const float* po = p.sc.part_o + ((long long)first * p.q_heads + head) * kHeadDim + d;
+  const long long stride = (long long)p.q_heads * kHeadDim;
+  float acc = 0.f;
+  const int staged = n < kMaxStaged ? n : kMaxStaged;
+#pragma unroll 8
+  for (int i = 0; i < staged; ++i) acc += po[i * stride] * weight_s[i];
+  for (int i = staged; i < n; ++i) acc += po[i * stride] * exp2f(pm[(long long)i * p.q_heads] - mmax);
   orow[d] = from_float<T>(acc / fmaxf(lsum, 1.17549435e-38f));
 }
 
@@ -474,6 +511,8 @@ __global__ void generic_decode_kernel(View4 q, View4 out, View4 kb, View4 vb, In
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
+}  // namespace
+
 struct MapKey {
   void* ptr;
   long long s0, s1, s2;
@@ -529,6 +568,8 @@ bool pages_fit_tma(const mie_view4_t& v, int head_dim, int block_size) {
   }
   return true;
 }
+
+namespace {
 
 constexpr size_t kDecodeSmem = (size_t)kWarps * kStages * kStageBytes + kWarps * kStages * 8 +
                                (size_t)kWarps * kPidBatch * 4 + 1024;

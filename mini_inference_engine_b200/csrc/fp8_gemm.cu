@@ -21,9 +21,9 @@
 //   * Persistent stream-K schedule: the (tile, K block) iteration space is cut
 //     into gridDim.x equal contiguous ranges, so every SM streams the same
 //     number of bytes whatever the shape.  A CTA that owns only part of a
-//     tile's K range writes an fp32 partial; the last contributor to arrive
-//     (an atomic ticket, never a spin) sums the partials in a fixed order, so
-//     results are deterministic.
+//     tile's K range writes an fp32 partial, and a small fix-up kernel sums
+//     the partials of each split tile in a fixed order (no atomics, no flags,
+//     no waiting), so results are deterministic.
 //   * Every mbarrier wait is bounded; a wait that runs out sets
 //     MIE_STATUS_WAIT_TIMEOUT, the roles fall through to the common exit and
 //     TMEM is released.
@@ -38,7 +38,6 @@ namespace {
 constexpr int kTileR = 128;  // UMMA M
 constexpr int kBlockK = 128; // bytes of K per pipeline stage = one scale block
 constexpr int kUmmaK = 32;   // fp8 elements per tcgen05.mma
-constexpr int kCounterInts = 1 << 16;  // tile counters at the front of the workspace
 
 // --------------------------------------------------------------------------
 // tcgen05 wrappers
@@ -137,26 +136,51 @@ struct GemmParams {
   long long ldy;
   int out_f16;
   float* workspace;       // [2 * gridDim.x][BN][128] fp32 partial tiles
-  int* tile_counters;     // [tiles], zero between launches
   int* status;
+  long long* trace;       // optional [gridDim.x][16] globaltimer stamps (profiling aid), or null
 };
 
-template <int BN, int E>
+__device__ __forceinline__ void trace_stamp(const GemmParams& p, int slot) {
+  if (p.trace != nullptr) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    p.trace[(size_t)blockIdx.x * 16 + slot] = (long long)t;
+  }
+}
+
+// Scale staging: per chunk of kChunkKb K blocks the epilogue warps pull every
+// scale they will need into shared memory in one batch, so no global-memory
+// latency sits between two K blocks.
+template <int BN, bool kSwap>
+struct ScaleStage {
+  static constexpr int kWidth = kSwap ? BN : kTileR;             // token scales per K block
+  static constexpr int kChunkKb = kSwap ? (4096 / BN > 32 ? 32 : 4096 / BN) : 16;
+  static constexpr int kWBlocks = kSwap ? 1 : (BN + 127) / 128;  // weight scale blocks per tile column range
+  static constexpr int kFloats = kChunkKb * kWidth + kChunkKb * kWBlocks;
+};
+
+template <int BN, int E, bool kSwap>
 struct GemmSmem {
   static constexpr int kStageBytes = kTileR * kBlockK + BN * kBlockK;
-  static constexpr int kStages = (200 * 1024 / kStageBytes) > 12 ? 12 : (200 * 1024 / kStageBytes);
-  static constexpr int kBarBytes = (2 * kStages + 4) * 8;
-  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + 2 * BN * 4 + 64 + 1024;
+  static constexpr int kScaleBytes = ScaleStage<BN, kSwap>::kFloats * 4;
+  static constexpr int kBudget = 200 * 1024 - kScaleBytes;
+  static constexpr int kStages = (kBudget / kStageBytes) > 12 ? 12 : (kBudget / kStageBytes);
+  static constexpr int kBarBytes = (2 * kStages + 16) * 8;
+  static constexpr int kTotal = kStages * kStageBytes + kBarBytes + kScaleBytes + 64 + 1024;
 };
 
 template <int BN, int E, bool kSwap>
 __global__ void __launch_bounds__((E + 2) * 32, 1)
     fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_c,
                     const GemmParams p) {
-  using S = GemmSmem<BN, E>;
+  using S = GemmSmem<BN, E, kSwap>;
+  using SS = ScaleStage<BN, kSwap>;
   constexpr int kStages = S::kStages;
   constexpr int kCols = E == 8 ? BN / 2 : BN;  // accumulator columns owned by one epilogue warp
-  constexpr uint32_t kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+  // Accumulator ring in TMEM: as many BN-column buffers as fit (at most 8), so the MMA issuer can run
+  // several K blocks ahead of the promotion.
+  constexpr int kAcc = 512 / BN > 8 ? 8 : 512 / BN;
+  constexpr uint32_t kTmemCols = kAcc * BN < 32 ? 32 : kAcc * BN;
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
   static_assert(kCols % 16 == 0, "column slice must be a multiple of 16");
 
@@ -166,10 +190,9 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full = empty_bar + kStages;
-  uint64_t* tmem_empty = tmem_full + 2;
-  float* svec = reinterpret_cast<float*>(tmem_empty + 2);  // [2][BN] combined scales (swapped mode)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(svec + 2 * BN);
-  int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);
+  uint64_t* tmem_empty = tmem_full + 8;
+  float* sscale = reinterpret_cast<float*>(tmem_empty + 8);  // staged scales of the current K chunk
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sscale + SS::kFloats);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb_total = (p.k + kBlockK - 1) / kBlockK;
@@ -179,12 +202,13 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
   const int G = gridDim.x;
   const long long it_begin = iters * blockIdx.x / G, it_end = iters * (blockIdx.x + 1) / G;
 
+  if (threadIdx.x == 0) trace_stamp(p, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < kAcc; ++b) {
       mbar_init(&tmem_full[b], 1);
       mbar_init(&tmem_empty[b], E);
     }
@@ -200,10 +224,12 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) trace_stamp(p, 1);
 
   if (warp == E) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
+      const uint64_t stream_policy = l2_evict_first_policy();
       uint32_t n = 0;
       for (long long it = it_begin; it < it_end; ++it, ++n) {
         const int tile = (int)(it / kb_total), kb = (int)(it % kb_total);
@@ -215,9 +241,14 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
         }
         uint8_t* dst = stage_base + (size_t)s * S::kStageBytes;
         mbar_expect_tx(&full_bar[s], S::kStageBytes);
-        tma_load_2d(dst, &map_r, &full_bar[s], kb * kBlockK, tr * kTileR);
+        if (kSwap)  // decode-time weights are streamed once: keep them from flushing L2
+          tma_load_2d_hint(dst, &map_r, &full_bar[s], kb * kBlockK, tr * kTileR, stream_policy);
+        else
+          tma_load_2d(dst, &map_r, &full_bar[s], kb * kBlockK, tr * kTileR);
         tma_load_2d(dst + kTileR * kBlockK, &map_c, &full_bar[s], kb * kBlockK, tc * BN);
+        if (n == 0) trace_stamp(p, 2);
       }
+      trace_stamp(p, 3);
     }
   } else if (warp == E + 1) {
     // ---------------- MMA issuer ----------------
@@ -225,13 +256,14 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
       constexpr uint32_t idesc = instr_desc_f8(BN);
       uint32_t n = 0;
       for (long long it = it_begin; it < it_end; ++it, ++n) {
-        const int s = n % kStages, b = n & 1;
+        const int s = n % kStages, b = n % kAcc;
         if (!mbar_wait_bounded(&full_bar[s], (n / kStages) & 1u) ||
-            !mbar_wait_bounded(&tmem_empty[b], ((n >> 1) & 1u) ^ 1u)) {
+            !mbar_wait_bounded(&tmem_empty[b], ((n / kAcc) & 1u) ^ 1u)) {
           raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
           break;
         }
         tc_fence_after();
+        if (n == 0) trace_stamp(p, 4);
         const uint32_t a_addr = smem_u32(stage_base + (size_t)s * S::kStageBytes);
         const uint32_t b_addr = a_addr + kTileR * kBlockK;
         const uint64_t da = smem_desc_k128(a_addr), db = smem_desc_k128(b_addr);
@@ -243,6 +275,7 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
         umma_commit(&empty_bar[s]);  // frees the smem stage once these MMAs have read it
         umma_commit(&tmem_full[b]);  // hands the K block's accumulator to the epilogue
       }
+      trace_stamp(p, 5);
     }
   } else {
     // ---------------- Epilogue warps ----------------
@@ -269,98 +302,91 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
       const int r_glob = tr * kTileR + row_in_tile;  // token (normal) or weight row (swapped)
       const int wblk = kSwap ? tr : (tc * BN + col0) / 128;  // weight scale block of this warp's slice
 
-      for (int kb = kb_first; kb < kb_last && ok; ++kb, ++n) {
-        const int b = n & 1;
-        float s_row = 0.f;
+      for (int kb0 = kb_first; kb0 < kb_last && ok; kb0 += SS::kChunkKb) {
+        const int kc = kb_last - kb0 < SS::kChunkKb ? kb_last - kb0 : SS::kChunkKb;
+        // Stage this chunk's scales (all loads in flight together).
+        epi_bar_sync(epi_threads);  // the previous chunk's readers are done
+        float* s_w = sscale + SS::kChunkKb * SS::kWidth;
         if (kSwap) {
-          // svec[c] = a_scale[token c] * w_scale, shared by all epilogue threads.
-          const float ws = p.w_scale[(long long)wblk * p.w_scale_ld + kb];
-          for (int c = epi_tid; c < BN; c += epi_threads) {
-            const int tok = tc * BN + c;
-            svec[b * BN + c] = tok < p.m ? p.a_scale[(long long)kb * p.a_scale_ld + tok] * ws : 0.f;
+          // Products a_scale[token] * w_scale, one per (K block, column).
+          for (int i = epi_tid; i < kc * BN; i += epi_threads) {
+            const int kk = i / BN, tok = tc * BN + i % BN;
+            const float ws = p.w_scale[(long long)wblk * p.w_scale_ld + kb0 + kk];
+            sscale[i] = tok < p.m ? p.a_scale[(long long)(kb0 + kk) * p.a_scale_ld + tok] * ws : 0.f;
           }
-          epi_bar_sync(epi_threads);
         } else {
-          const float ws = p.w_scale[(long long)wblk * p.w_scale_ld + kb];
-          s_row = r_glob < p.m ? p.a_scale[(long long)kb * p.a_scale_ld + r_glob] * ws : 0.f;
+          for (int i = epi_tid; i < kc * kTileR; i += epi_threads) {
+            const int kk = i / kTileR, tok = tr * kTileR + i % kTileR;
+            sscale[i] = tok < p.m ? p.a_scale[(long long)(kb0 + kk) * p.a_scale_ld + tok] : 0.f;
+          }
+          for (int i = epi_tid; i < kc * SS::kWBlocks; i += epi_threads) {
+            const int kk = i / SS::kWBlocks, blk = (tc * BN) / 128 + i % SS::kWBlocks;
+            s_w[i] = blk * 128 < p.n ? p.w_scale[(long long)blk * p.w_scale_ld + kb0 + kk] : 0.f;
+          }
         }
-        if (!mbar_wait_bounded(&tmem_full[b], (n >> 1) & 1u)) {
-          raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t taddr = lane_addr + (uint32_t)(b * BN + col0);
-        if constexpr (kCols % 32 == 0) {
+        epi_bar_sync(epi_threads);
+        if (epi_tid == 0 && n == 0) trace_stamp(p, 6);
+        for (int kk = 0; kk < kc; ++kk, ++n) {
+          const int b = n % kAcc;
+          float s_row = 0.f;
+          if (!kSwap) s_row = sscale[kk * kTileR + row_in_tile] * s_w[kk * SS::kWBlocks + (col0 / 128)];
+          const float* s_col = sscale + kk * BN + col0;  // swapped mode: one product per column
+          if (!mbar_wait_bounded(&tmem_full[b], (n / kAcc) & 1u)) {
+            raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          if (epi_tid == 0 && n == 0) trace_stamp(p, 7);
+          const uint32_t taddr = lane_addr + (uint32_t)(b * BN + col0);
+          if constexpr (kCols % 64 == 0) {
+            // Two loads in flight per wait: halves the TMEM round trips per K block.
 #pragma unroll
-          for (int c = 0; c < kCols; c += 32) {
-            float d[32];
-            tmem_ld32(taddr + c, d);
+            for (int c = 0; c < kCols; c += 64) {
+              float d0[32], d1[32];
+              tmem_ld32(taddr + c, d0);
+              tmem_ld32(taddr + c + 32, d1);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(d0[j], kSwap ? s_col[c + j] : s_row, acc[c + j]);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                acc[c + 32 + j] = fmaf(d1[j], kSwap ? s_col[c + 32 + j] : s_row, acc[c + 32 + j]);
+            }
+          } else if constexpr (kCols % 32 == 0) {
+#pragma unroll
+            for (int c = 0; c < kCols; c += 32) {
+              float d[32];
+              tmem_ld32(taddr + c, d);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(d[j], kSwap ? s_col[c + j] : s_row, acc[c + j]);
+            }
+          } else {
+            float d[16];
+            tmem_ld16(taddr, d);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float s = kSwap ? svec[b * BN + col0 + c + j] : s_row;
-              acc[c + j] = fmaf(d[j], s, acc[c + j]);
-            }
+            for (int j = 0; j < 16; ++j) acc[j] = fmaf(d[j], kSwap ? s_col[j] : s_row, acc[j]);
           }
-        } else {
-          float d[16];
-          tmem_ld16(taddr, d);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float s = kSwap ? svec[b * BN + col0 + j] : s_row;
-            acc[j] = fmaf(d[j], s, acc[j]);
-          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[b]);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tmem_empty[b]);
       }
       if (!ok) break;
 
-      // ---- segment done: direct store, or partial + last-arriver reduction ----
+      // ---- segment done: a whole tile is stored directly; a partial K range goes to the workspace
+      //      and the fix-up kernel sums the contributions of each split tile in a fixed order ----
+      if (epi_tid == 0 && it == it_begin) trace_stamp(p, 8);
       const bool whole = kb_first == 0 && kb_last == kb_total;
-      bool do_store = whole;
+      const bool do_store = whole;
       if (!whole) {
         const int slot = it == it_begin ? 0 : 1;
         float* ws_tile = p.workspace + ((size_t)blockIdx.x * 2 + slot) * (size_t)(BN * kTileR);
 #pragma unroll
         for (int j = 0; j < kCols; ++j) ws_tile[(size_t)(col0 + j) * kTileR + row_in_tile] = acc[j];
-        __threadfence();
-        epi_bar_sync(epi_threads);
-        if (epi_tid == 0) {
-          // Contributors of this tile = CTAs whose ranges intersect it.
-          const long long t0 = tile_it0, t1 = tile_it0 + kb_total;
-          int c_first = (int)((t0 * G) / iters);
-          while (iters * (c_first + 1) / G <= t0) ++c_first;
-          while (c_first > 0 && iters * c_first / G > t0) --c_first;
-          int c_last = c_first;
-          while (iters * (c_last + 1) / G < t1) ++c_last;
-          const int contributors = c_last - c_first + 1;
-          const int old = atomicAdd(&p.tile_counters[tile], 1);
-          const bool last = old == contributors - 1;
-          if (last) p.tile_counters[tile] = 0;
-          last_flag[0] = last ? 1 : 0;
-          last_flag[1] = c_first;
-          last_flag[2] = c_last;
-        }
-        epi_bar_sync(epi_threads);
-        if (last_flag[0]) {
-          __threadfence();
-          const int c_first = last_flag[1], c_last = last_flag[2];
-#pragma unroll
-          for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
-          for (int c = c_first; c <= c_last; ++c) {
-            const long long r0 = iters * c / G;
-            const int cslot = (r0 >= tile_it0) ? 0 : 1;  // a segment that opens its CTA's range is slot 0
-            const float* src = p.workspace + ((size_t)c * 2 + cslot) * (size_t)(BN * kTileR);
-#pragma unroll
-            for (int j = 0; j < kCols; ++j) acc[j] += __ldcg(&src[(size_t)(col0 + j) * kTileR + row_in_tile]);
-          }
-          do_store = true;
-        }
-        epi_bar_sync(epi_threads);  // last_flag is reused by the next segment
+        if (epi_tid == 0 && it == it_begin) trace_stamp(p, 9);
       }
       if (do_store) {
         if (kSwap) {
@@ -408,6 +434,7 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
       }
       it = seg_end;
     }
+    if (epi_tid == 0) trace_stamp(p, 11);
   }
 
   tc_fence_before();
@@ -415,6 +442,66 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
   if (warp == E + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0) trace_stamp(p, 12);
+}
+
+// --------------------------------------------------------------------------
+// Fix-up: sums the fp32 partials of every tile whose K range was shared by several CTAs.
+// grid = (tiles, BN / 16); 128 threads = the tile's rows; each block owns 16 columns.
+// The contributors of a tile and their workspace slots follow from the same arithmetic
+// the GEMM kernel uses, so no flags or counters are exchanged.
+// --------------------------------------------------------------------------
+template <int BN, bool kSwap>
+__global__ void __launch_bounds__(kTileR) fp8_gemm_fixup_kernel(const GemmParams p, int G) {
+  const int kb_total = (p.k + kBlockK - 1) / kBlockK;
+  const int tiles_r = (p.rows_r + kTileR - 1) / kTileR;
+  const int tiles_c = (p.rows_c + BN - 1) / BN;
+  const long long iters = (long long)tiles_r * tiles_c * kb_total;
+  const int tile = blockIdx.x, cchunk = blockIdx.y * 16, row = threadIdx.x;
+  const long long t0 = (long long)tile * kb_total, t1 = t0 + kb_total;
+  int c_first = (int)((t0 * G) / iters);
+  while (iters * (c_first + 1) / G <= t0) ++c_first;
+  while (c_first > 0 && iters * c_first / G > t0) --c_first;
+  int c_last = c_first;
+  while (iters * (c_last + 1) / G < t1) ++c_last;
+  if (c_last == c_first) return;  // one CTA had the whole K range and stored the tile itself
+  float acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+  for (int c = c_first; c <= c_last; ++c) {
+    const long long r0 = iters * c / G;
+    const int slot = r0 >= t0 ? 0 : 1;  // a segment that opens its CTA's range is slot 0
+    const float* src = p.workspace + ((size_t)c * 2 + slot) * (size_t)(BN * kTileR);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) acc[j] += src[(size_t)(cchunk + j) * kTileR + row];
+  }
+  const int tr = tile % tiles_r, tc = tile / tiles_r;
+  const int r_glob = tr * kTileR + row;
+  if (kSwap) {
+    if (r_glob >= p.n) return;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int tok = tc * BN + cchunk + j;
+      if (tok < p.m) {
+        if (p.out_f16)
+          reinterpret_cast<__half*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2half_rn(acc[j]);
+        else
+          reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2bfloat16_rn(acc[j]);
+      }
+    }
+  } else {
+    if (r_glob >= p.m) return;
+    const int n0 = tc * BN + cchunk;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      if (n0 + j < p.n) {
+        if (p.out_f16)
+          reinterpret_cast<__half*>(p.y)[(long long)r_glob * p.ldy + n0 + j] = __float2half_rn(acc[j]);
+        else
+          reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)r_glob * p.ldy + n0 + j] = __float2bfloat16_rn(acc[j]);
+      }
+    }
   }
 }
 
@@ -520,7 +607,7 @@ int operand_map(const void* ptr, long long rows, long long k, long long ld, int 
 
 template <int BN, int E, bool kSwap>
 int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& p, int grid, cudaStream_t stream) {
-  using S = GemmSmem<BN, E>;
+  using S = GemmSmem<BN, E, kSwap>;
   static bool configured[64] = {false};
   int dev = 0;
   MIE_CUDA(cudaGetDevice(&dev));
@@ -531,6 +618,11 @@ int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& 
   }
   fp8_gemm_kernel<BN, E, kSwap><<<grid, (E + 2) * 32, S::kTotal, stream>>>(mr, mc, p);
   MIE_LAUNCH_CHECK("fp8_gemm_kernel");
+  const long long tiles = (long long)((p.rows_r + kTileR - 1) / kTileR) * ((p.rows_c + BN - 1) / BN);
+  if (tiles % grid != 0) {  // otherwise every CTA range is a whole number of tiles
+    fp8_gemm_fixup_kernel<BN, kSwap><<<dim3((unsigned)tiles, BN / 16), kTileR, 0, stream>>>(p, grid);
+    MIE_LAUNCH_CHECK("fp8_gemm_fixup_kernel");
+  }
   return MIE_OK;
 }
 
@@ -546,8 +638,8 @@ extern "C" int64_t mie_fp8_gemm_workspace_bytes(int32_t m, int32_t n, int32_t k)
   (void)n;
   (void)k;
   const int bn = m <= 128 ? swap_bn(m) : 256;
-  // One int32 counter per tile (a fixed block of 65536) followed by two fp32 partial tiles per CTA.
-  return (long long)kCounterInts * 4 + (long long)sm_count() * 2 * bn * kTileR * 4;
+  // Two fp32 partial tiles per persistent CTA.
+  return (long long)sm_count() * 2 * bn * kTileR * 4;
 }
 
 extern "C" int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t ldq, float* scales,
@@ -572,7 +664,8 @@ extern "C" int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void*
 extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
                             int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy,
                             int32_t out_dtype, int32_t m, int32_t n, int32_t k, void* workspace,
-                            int64_t workspace_bytes, int32_t* status, void* stream_) {
+                            int64_t workspace_bytes, int32_t grid_limit, int32_t* status, int64_t* trace,
+                            void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MIE_CHECK_ARG(x8 && a_scale && w8 && w_scale && y && workspace, "null pointer");
   MIE_CHECK_ARG(m >= 0 && n >= 1 && k >= 1, "invalid GEMM shape %d x %d x %d", m, n, k);
@@ -591,9 +684,10 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
   const long long tiles = tiles_r * tiles_c;
   const long long iters = tiles * kb;
   const int sms = sm_count();
-  const int grid = (int)(iters < sms ? iters : sms);
-  const long long need = (long long)kCounterInts * 4 + (long long)grid * 2 * bn * kTileR * 4;
-  MIE_CHECK_ARG(tiles <= kCounterInts, "too many output tiles (%lld)", tiles);
+  int grid = (int)(iters < sms ? iters : sms);
+  if (grid_limit > 0 && grid_limit < grid) grid = grid_limit;
+  const long long need = (long long)grid * 2 * bn * kTileR * 4;
+  MIE_CHECK_ARG(tiles <= 0x7fffffff / 2, "too many output tiles (%lld)", tiles);
   MIE_CHECK_ARG(workspace_bytes >= need, "workspace of %lld bytes is too small (need %lld)",
                 (long long)workspace_bytes, need);
   MIE_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
@@ -611,11 +705,9 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
   p.y = y;
   p.ldy = ldy;
   p.out_f16 = out_dtype == MIE_DTYPE_F16;
-  // Counters sit at the front so their position does not depend on the shape;
-  // they must be zero before the first launch and are left zero by every launch.
-  p.tile_counters = reinterpret_cast<int*>(workspace);
-  p.workspace = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + (size_t)kCounterInts * 4);
+  p.workspace = reinterpret_cast<float*>(workspace);
   p.status = status;
+  p.trace = reinterpret_cast<long long*>(trace);
 
   CUtensorMap mr, mc;
   if (swap) {

@@ -1,0 +1,210 @@
+"""Fused RMSNorm / SiLU*up / RoPE (reference: engine/kernels/fused.py).
+
+Same function names and call signatures as the reference; the kernels are in
+``csrc/fused_glue.cu``.  The bf16 rounding points are PyTorch's (fp32 math in
+between); the row-sum order of RMSNorm is a plain warp/CTA tree rather than
+ATen's, so results agree with the unfused ops to within one bf16 ulp on rare
+elements instead of bit for bit.
+"""
+
+from __future__ import annotations
+
+import types
+from typing import Any
+
+import torch
+
+from ... import _lib
+
+
+def fused_kernels_available(device: torch.device | str | None = None) -> bool:
+    if not torch.cuda.is_available() or (device is not None and torch.device(device).type != "cuda"):
+        return False
+    _lib.load()
+    return True
+
+
+def _rows_2d(x: torch.Tensor, n_cols: int) -> torch.Tensor | None:
+    """``x`` as ``[rows, n_cols]`` without a copy, or None when the rows are not evenly strided."""
+
+    try:
+        rows = x.view(-1, n_cols)
+    except RuntimeError:
+        return None
+    return rows if rows.stride(-1) == 1 and rows.stride(0) % 8 == 0 and rows.data_ptr() % 16 == 0 else None
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float,
+             residual: torch.Tensor | None = None) -> torch.Tensor | tuple[torch.Tensor, torch.Tensor]:
+    """``Qwen3RMSNorm(x)``, or ``(norm(x + residual), x + residual)`` (engine/kernels/fused.py:165-203)."""
+
+    n_cols = int(x.shape[-1])
+    if n_cols % 4 or n_cols < 128:
+        raise ValueError("rms_norm reproduces PyTorch's vectorized reduction: width must be a multiple of 4, >= 128")
+    if x.dtype != torch.bfloat16 or not x.is_cuda:
+        raise ValueError("rms_norm expects a CUDA bf16 tensor")
+    lib = _lib.load()
+    stream = _lib.stream_arg(x.device)
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    weight = weight.contiguous()
+    rows = _rows_2d(x, n_cols)
+    if rows is None and residual is None and n_cols == 128 and x.dim() >= 3 and x.stride(-1) == 1:
+        # Per-head rows of a [..., heads, 128] column view of a merged q/k/v output.
+        view = x.reshape(-1, int(x.shape[-2]), n_cols) if x.dim() > 3 else x
+        if view.stride(-1) == 1 and view.stride(0) % 8 == 0 and view.stride(1) % 8 == 0 and view.data_ptr() % 16 == 0:
+            _lib.check(lib.mie_head_rms_norm(_lib.ptr(view), view.stride(0), view.stride(1), int(view.shape[1]),
+                                             _lib.ptr(weight), _lib.ptr(out), view.shape[0] * view.shape[1],
+                                             float(eps), stream))
+            return out
+    if rows is None or n_cols % 8 or n_cols > 8192:
+        rows = x.contiguous().view(-1, n_cols)
+        if n_cols % 8 or n_cols > 8192:
+            raise ValueError("rms_norm supports widths that are multiples of 8 up to 8192")
+    num_rows = int(rows.shape[0])
+    if residual is None:
+        _lib.check(lib.mie_rms_norm(_lib.ptr(rows), rows.stride(0), None, None, _lib.ptr(weight), _lib.ptr(out),
+                                    None, 0, None, 0, num_rows, n_cols, float(eps), stream))
+        return out
+    residual_rows = residual.reshape(-1, n_cols).contiguous()
+    summed = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    _lib.check(lib.mie_rms_norm(_lib.ptr(rows), rows.stride(0), _lib.ptr(residual_rows), _lib.ptr(summed),
+                                _lib.ptr(weight), _lib.ptr(out), None, 0, None, 0, num_rows, n_cols, float(eps),
+                                stream))
+    return out, summed
+
+
+def silu_mul(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """``F.silu(gate) * up`` in one pass (engine/kernels/fused.py:217-233)."""
+
+    n_cols = int(gate.shape[-1])
+    gate_rows, up_rows = _rows_2d(gate, n_cols), _rows_2d(up, n_cols)
+    if gate_rows is None or up_rows is None or gate_rows.stride() != up_rows.stride() or n_cols % 8:
+        gate_rows, up_rows = gate.contiguous().view(-1, n_cols), up.contiguous().view(-1, n_cols)
+        if n_cols % 8:
+            raise ValueError("silu_mul supports widths that are multiples of 8")
+    out = torch.empty(gate.shape, dtype=gate.dtype, device=gate.device)
+    _lib.check(_lib.load().mie_silu_mul(_lib.ptr(gate_rows), _lib.ptr(up_rows), gate_rows.stride(0), _lib.ptr(out),
+                                        None, 0, None, 0, int(gate_rows.shape[0]), n_cols,
+                                        _lib.stream_arg(gate.device)))
+    return out
+
+
+def _rope_one(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    batch, heads, seq, dim = x.shape
+    out = torch.empty_like(x)
+    _lib.check(_lib.load().mie_rope(_lib.view4_arg(x), _lib.ptr(cos), _lib.ptr(sin),
+                                    cos.stride(0) if cos.shape[0] > 1 else 0, cos.stride(1), _lib.view4_arg(out),
+                                    batch, heads, seq, dim, _lib.stream_arg(x.device)))
+    return out
+
+
+def apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1):
+    """Drop-in for ``transformers.models.qwen3.modeling_qwen3.apply_rotary_pos_emb`` (fused.py:247-262)."""
+
+    supported = (
+        unsqueeze_dim == 1 and q.is_cuda and q.dim() == 4 and k.dim() == 4 and cos.dim() == 3
+        and q.dtype == k.dtype == cos.dtype == sin.dtype == torch.bfloat16
+        and q.stride(-1) == 1 and k.stride(-1) == 1 and cos.stride(-1) == 1 and sin.stride() == cos.stride()
+        and q.shape[-1] % 2 == 0 and cos.shape[0] in (1, q.shape[0]) and cos.shape[1] == q.shape[2]
+    )
+    if not supported:
+        raise ValueError("apply_rotary_pos_emb: unsupported layout (bf16 CUDA [B, H, T, D] with [B|1, T, D] cos/sin)")
+    return _rope_one(q, cos, sin), _rope_one(k, cos, sin)
+
+
+# --- Installation on a Hugging Face Qwen3 model -------------------------------------------------
+
+_ORIGINAL_ROPE: Any = None
+_ROPE_INSTALLS = 0
+
+
+def _fusable_norm(hidden_states: torch.Tensor) -> bool:
+    width = int(hidden_states.shape[-1])
+    return hidden_states.dtype == torch.bfloat16 and hidden_states.is_cuda and width % 8 == 0 and 128 <= width <= 8192
+
+
+def _norm_forward(self, hidden_states):
+    if not _fusable_norm(hidden_states):
+        return type(self).forward(self, hidden_states)
+    return rms_norm(hidden_states, self.weight, self.variance_epsilon)
+
+
+def _mlp_forward(self, x):
+    from .merged_projections import project_gate_up
+
+    return self.down_proj(silu_mul(*project_gate_up(self, x)))
+
+
+def _decoder_forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_values=None,
+                     use_cache=False, position_embeddings=None, **kwargs):
+    """Qwen3DecoderLayer.forward with the post-attention residual add folded into the next RMSNorm."""
+
+    residual = hidden_states
+    hidden_states, _ = self.self_attn(
+        hidden_states=self.input_layernorm(hidden_states), attention_mask=attention_mask,
+        position_ids=position_ids, past_key_values=past_key_values, use_cache=use_cache,
+        position_embeddings=position_embeddings, **kwargs,
+    )
+    norm = self.post_attention_layernorm
+    if _fusable_norm(hidden_states):
+        hidden_states, residual = rms_norm(hidden_states, norm.weight, norm.variance_epsilon, residual=residual)
+    else:
+        residual = residual + hidden_states
+        hidden_states = norm(residual)
+    return residual + self.mlp(hidden_states)
+
+
+def warm_fused_kernels(model: Any) -> None:
+    """Nothing is compiled at run time here; kept so callers of the reference API need no change."""
+
+    del model
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+
+
+def install_fused_kernels(model: Any) -> bool:
+    """Route a HF Qwen3 model's norms, MLPs, layer adds and RoPE through these kernels (fused.py:350-382)."""
+
+    global _ORIGINAL_ROPE, _ROPE_INSTALLS
+    if getattr(model, "_minillm_fused_kernels", False):
+        return True
+    if not fused_kernels_available(next(model.parameters()).device):
+        return False
+    from transformers.models.qwen3 import modeling_qwen3
+
+    overrides = {
+        modeling_qwen3.Qwen3RMSNorm: _norm_forward,
+        modeling_qwen3.Qwen3MLP: _mlp_forward,
+        modeling_qwen3.Qwen3DecoderLayer: _decoder_forward,
+    }
+    for module in model.modules():
+        for cls, forward in overrides.items():
+            if isinstance(module, cls):
+                module.forward = types.MethodType(forward, module)
+    if _ROPE_INSTALLS == 0:
+        _ORIGINAL_ROPE = modeling_qwen3.apply_rotary_pos_emb
+        modeling_qwen3.apply_rotary_pos_emb = apply_rotary_pos_emb
+    _ROPE_INSTALLS += 1
+    model._minillm_fused_kernels = True
+    return True
+
+
+def uninstall_fused_kernels(model: Any) -> None:
+    global _ROPE_INSTALLS
+    if not getattr(model, "_minillm_fused_kernels", False):
+        return
+    from transformers.models.qwen3 import modeling_qwen3
+
+    for module in model.modules():
+        if isinstance(module, (modeling_qwen3.Qwen3RMSNorm, modeling_qwen3.Qwen3MLP, modeling_qwen3.Qwen3DecoderLayer)):
+            module.__dict__.pop("forward", None)
+    _ROPE_INSTALLS -= 1
+    if _ROPE_INSTALLS == 0:
+        modeling_qwen3.apply_rotary_pos_emb = _ORIGINAL_ROPE
+    model._minillm_fused_kernels = False
+
+
+__all__ = [
+    "apply_rotary_pos_emb", "fused_kernels_available", "install_fused_kernels",
+    "rms_norm", "silu_mul", "uninstall_fused_kernels", "warm_fused_kernels",
+]

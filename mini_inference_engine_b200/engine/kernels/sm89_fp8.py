@@ -191,7 +191,8 @@ def _gemm_weight(weight: torch.Tensor) -> torch.Tensor:
 
 def launch_fp8_gemm(quantized: torch.Tensor, scales_kmajor: torch.Tensor, weight: torch.Tensor,
                     weight_scale_inv: torch.Tensor, output: torch.Tensor, m: int, k: int,
-                    status: torch.Tensor | None = None) -> None:
+                    status: torch.Tensor | None = None, grid_limit: int = 0,
+                    trace: torch.Tensor | None = None) -> None:
     """``output[m, n] = fp8 block-scaled product``; thin call into ``mie_fp8_gemm``."""
 
     device = output.device
@@ -203,7 +204,8 @@ def launch_fp8_gemm(quantized: torch.Tensor, scales_kmajor: torch.Tensor, weight
         _lib.ptr(quantized), quantized.stride(0), _lib.ptr(scales_kmajor), scales_kmajor.stride(0),
         _lib.ptr(w), w.stride(0), _lib.ptr(scales_w), scales_w.stride(0),
         _lib.ptr(output), output.stride(0), _lib.DTYPE_CODES[output.dtype], m, int(weight.shape[0]), k,
-        _lib.ptr(workspace), workspace.numel(), _lib.ptr(word), _lib.stream_arg(device),
+        _lib.ptr(workspace), workspace.numel(), int(grid_limit), _lib.ptr(word), _lib.ptr(trace),
+        _lib.stream_arg(device),
     ))
 
 
