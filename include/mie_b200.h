@@ -67,6 +67,8 @@ const char* mie_last_error(void);
 int mie_version(void);
 /* Number of SMs of the current device (used by callers to size scratch). */
 int mie_sm_count(void);
+/* Kernels this library has launched (or captured into a graph) in this process so far. */
+int64_t mie_launch_count(void);
 
 /* ------------------------------------------------------------------------
  * KV-cache scatter

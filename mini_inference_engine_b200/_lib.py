@@ -51,6 +51,7 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "mie_last_error": (c_char_p, []),
     "mie_version": (ctypes.c_int, []),
     "mie_sm_count": (ctypes.c_int, []),
+    "mie_launch_count": (c_int64, []),
     "mie_write_decode_kv": (ctypes.c_int, [View4T, View4T, IndexT, IndexT, IndexT, View4T, View4T, c_int32, c_int32,
                                            c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p, c_void_p]),
     "mie_write_packed_kv": (ctypes.c_int, [View4T, View4T, IndexT, IndexT, IndexT, View4T, View4T, c_int32, c_int32,

@@ -39,9 +39,11 @@ int cuda_fail(cudaError_t err, const char* what);
   do {                                                          \
     cudaError_t err__ = cudaGetLastError();                     \
     if (err__ != cudaSuccess) return ::mie::cuda_fail(err__, name); \
+    ::mie::count_launch();                                      \
   } while (0)
 
 int sm_count();
+void count_launch();  // every kernel launch of this library bumps a host-side counter
 
 // ---------------------------------------------------------------------------
 // Integer metadata views (int32 or int64, arbitrary element strides).

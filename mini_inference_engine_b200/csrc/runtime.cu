@@ -2,6 +2,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -21,6 +22,9 @@ int cuda_fail(cudaError_t err, const char* what) {
   set_error("CUDA error %d (%s) in %s", (int)err, cudaGetErrorString(err), what);
   return MIE_ERR_CUDA;
 }
+
+static std::atomic<long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int sm_count() {
   static int cached[64] = {0};
@@ -83,3 +87,4 @@ int make_tensor_map(CUtensorMap* out, CUtensorMapDataType dtype, int rank, void*
 extern "C" const char* mie_last_error(void) { return mie::g_error; }
 extern "C" int mie_version(void) { return 1; }
 extern "C" int mie_sm_count(void) { return mie::sm_count(); }
+extern "C" int64_t mie_launch_count(void) { return mie::g_launches.load(std::memory_order_relaxed); }

@@ -6,7 +6,7 @@ Takes the place of the captured decode forward of the reference
 (engine/model_runner/qwen3_mixed.py:125, qwen3_packed.py:29).  The reference
 drives Hugging Face's ``Qwen3ForCausalLM`` and monkey-patches its modules; this
 runner owns plain weight tensors and calls the kernels directly, so one decode
-layer is eight launches:
+layer is a dozen launches of this library's kernels:
 
   add+RMSNorm(+quant) -> FP8 GEMM (merged qkv) -> q/k-norm + RoPE + KV write ->
   paged decode attention -> quant -> FP8 GEMM (o) [all-reduce] ->
@@ -236,23 +236,19 @@ class Qwen3DecodeRunner:
             _lib.check(lib.mie_rms_norm(_lib.ptr(x), x.stride(0), _lib.ptr(residual), _lib.ptr(summed),
                                         _lib.ptr(weight), None, _lib.ptr(q), q.stride(0), _lib.ptr(scales),
                                         scales.stride(0), rows, cols, self.shape.rms_eps, stream))
-            self.launches_per_step += 1
             return None, summed, (q, scales)
         out = torch.empty_like(x)
         _lib.check(lib.mie_rms_norm(_lib.ptr(x), x.stride(0), _lib.ptr(residual), _lib.ptr(summed),
                                     _lib.ptr(weight), _lib.ptr(out), None, 0, None, 0, rows, cols,
                                     self.shape.rms_eps, stream))
-        self.launches_per_step += 1
         return out, summed, None
 
     def _gemm(self, quantized, weight, weight_scale, rows: int, k: int) -> torch.Tensor:
         out = torch.empty(rows, weight.shape[0], dtype=torch.bfloat16, device=self.device)
         sm89_fp8.launch_fp8_gemm(quantized[0], quantized[1], weight, weight_scale, out, rows, k, status=self.status)
-        self.launches_per_step += 1
         return out
 
     def _quantize(self, x: torch.Tensor):
-        self.launches_per_step += 1
         return sm89_fp8.quantize_activation_kmajor(x)
 
     def _all_reduce(self, x: torch.Tensor) -> torch.Tensor:
@@ -270,7 +266,7 @@ class Qwen3DecodeRunner:
         shape, lib = self.shape, _lib.load()
         stream = _lib.stream_arg(self.device)
         batch = int(input_ids.shape[0])
-        self.launches_per_step = 0
+        launches_before = lib.mie_launch_count()
         hd, lq, lkv = shape.head_dim, self.local_q_heads, self.local_kv_heads
         hidden = self.weights.embedding.index_select(0, input_ids)
         positions = sequence_lengths - 1
@@ -295,7 +291,6 @@ class Qwen3DecodeRunner:
                                     block_tables, sequence_lengths, None, scale=scale,
                                     max_total_tokens=batch * self.max_context, scratch=self.scratch,
                                     split_policy=1, use_plan=index > 0, plan_slot=index, status=self.status)
-            self.launches_per_step += 3 + (1 if index == 0 else 0)
             attn_q = self._quantize(attended.view(batch, lq * hd))
             attn_out = self._all_reduce(self._gemm(attn_q, layer.o, layer.o_scale, batch, lq * hd))
             _, residual, quantized = self._norm(attn_out, layer.post_norm, residual, quantize=True)
@@ -306,17 +301,16 @@ class Qwen3DecodeRunner:
                 _lib.check(lib.mie_silu_mul(_lib.ptr(gate_up), _lib.ptr(gate_up[:, inter:]), gate_up.stride(0), None,
                                             _lib.ptr(q), q.stride(0), _lib.ptr(scales), scales.stride(0), batch,
                                             inter, stream))
-                self.launches_per_step += 1
                 act_q = (q, scales)
             else:
                 act = torch.empty(batch, inter, dtype=torch.bfloat16, device=self.device)
                 _lib.check(lib.mie_silu_mul(_lib.ptr(gate_up), _lib.ptr(gate_up[:, inter:]), gate_up.stride(0),
                                             _lib.ptr(act), None, 0, None, 0, batch, inter, stream))
-                self.launches_per_step += 1
                 act_q = self._quantize(act)
             mlp_out = self._all_reduce(self._gemm(act_q, layer.down, layer.down_scale, batch, inter))
         final, _, _ = self._norm(mlp_out, self.weights.final_norm, residual, quantize=False)
         logits = torch.matmul(final, self.weights.lm_head.t())
+        self.launches_per_step = int(lib.mie_launch_count() - launches_before)
         if self.tp == 1:
             tokens = logits.argmax(dim=-1)
             return (tokens, logits) if return_logits else tokens
