@@ -206,10 +206,6 @@ int mie_flash_prefill_attention(const void* query, int64_t q_token_stride, int64
 int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t ldq, float* scales,
                      int32_t scale_ld, int32_t m, int32_t k, void* stream);
 
-/* Bytes of workspace (fp32 partial tiles of the stream-K schedule) mie_fp8_gemm needs;
- * the contents need not be initialised. */
-int64_t mie_fp8_gemm_workspace_bytes(int32_t m, int32_t n, int32_t k);
-
 /*
  * Replaces the GEMM of sm89_fp8_linear (engine/kernels/sm89_fp8.py:444-528;
  * kernels _fp8_linear_kernel :220-300 and _fp8_split_gemm_kernel :343-398):
@@ -218,14 +214,16 @@ int64_t mie_fp8_gemm_workspace_bytes(int32_t m, int32_t n, int32_t k);
  * x8 [m, k] e4m3 (row stride ldx bytes), a_scale as mie_fp8_quantize writes it,
  * w8 [n, k] e4m3 (row stride ldw bytes), w_scale [ceil(n/128), w_scale_ld].
  * Operand base pointers and row strides must be multiples of 16 bytes.
- * grid_limit > 0 caps the number of persistent CTAs (0: one per SM).  trace is a
- * profiling aid: NULL, or a device buffer of 16 int64 per CTA that receives
- * %globaltimer stamps of the kernel's phases.
+ * When a shape has fewer output tiles than SMs the K range of each tile is cut
+ * into up to 8 parts that run as one thread-block cluster and are summed in a
+ * fixed order through distributed shared memory; max_split > 0 caps that
+ * factor (1 = never split), 0 lets the library choose.  trace is a profiling
+ * aid: NULL, or a device buffer of 16 int64 per CTA that receives %globaltimer
+ * stamps of the kernel's phases.  Uses no global scratch memory.
  */
 int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
                  int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy, int32_t out_dtype,
-                 int32_t m, int32_t n, int32_t k, void* workspace, int64_t workspace_bytes, int32_t grid_limit,
-                 int32_t* status, int64_t* trace, void* stream);
+                 int32_t m, int32_t n, int32_t k, int32_t max_split, int32_t* status, int64_t* trace, void* stream);
 
 /* ------------------------------------------------------------------------
  * Fused memory-bound glue (bf16 activations)

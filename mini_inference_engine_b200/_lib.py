@@ -72,10 +72,9 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                                    c_void_p, c_void_p]),
     "mie_fp8_quantize": (ctypes.c_int, [c_void_p, c_int64, c_int32, c_void_p, c_int64, c_void_p, c_int32, c_int32,
                                         c_int32, c_void_p]),
-    "mie_fp8_gemm_workspace_bytes": (c_int64, [c_int32, c_int32, c_int32]),
     "mie_fp8_gemm": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_int32,
-                                    c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_void_p, c_int64,
-                                    c_int32, c_void_p, c_void_p, c_void_p]),
+                                    c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p,
+                                    c_void_p, c_void_p]),
     "mie_rms_norm": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                     c_void_p, c_int32, c_int32, c_int32, c_float, c_void_p]),
     "mie_head_rms_norm": (ctypes.c_int, [c_void_p, c_int64, c_int64, c_int32, c_void_p, c_void_p, c_int64, c_float,

@@ -18,12 +18,13 @@
 //     decode): the 128 UMMA rows are weight rows and the BN columns are tokens,
 //     so a handful of tokens still fills the tensor core's M and the kernel is
 //     a pure weight-streaming (HBM-bound) loop.
-//   * Persistent stream-K schedule: the (tile, K block) iteration space is cut
-//     into gridDim.x equal contiguous ranges, so every SM streams the same
-//     number of bytes whatever the shape.  A CTA that owns only part of a
-//     tile's K range writes an fp32 partial, and a small fix-up kernel sums
-//     the partials of each split tile in a fixed order (no atomics, no flags,
-//     no waiting), so results are deterministic.
+//   * Schedule: grid = (tiles, split).  When a shape has fewer output tiles
+//     than SMs (decode), the K range of every tile is cut into `split` (<= 8)
+//     parts that run as one thread-block cluster; each CTA parks its fp32
+//     partial in its own shared memory and, after a cluster barrier, reduces a
+//     slice of the tile by reading its peers through distributed shared
+//     memory in a fixed order (deterministic; no global partials, no atomics,
+//     no spinning).  With enough tiles split = 1 and CTAs store directly.
 //   * Every mbarrier wait is bounded; a wait that runs out sets
 //     MIE_STATUS_WAIT_TIMEOUT, the roles fall through to the common exit and
 //     TMEM is released.
@@ -135,16 +136,15 @@ struct GemmParams {
   void* y;                // [m][ldy] bf16 or fp16
   long long ldy;
   int out_f16;
-  float* workspace;       // [2 * gridDim.x][BN][128] fp32 partial tiles
   int* status;
-  long long* trace;       // optional [gridDim.x][16] globaltimer stamps (profiling aid), or null
+  long long* trace;       // optional [CTAs][16] globaltimer stamps (profiling aid), or null
 };
 
 __device__ __forceinline__ void trace_stamp(const GemmParams& p, int slot) {
   if (p.trace != nullptr) {
     unsigned long long t;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    p.trace[(size_t)blockIdx.x * 16 + slot] = (long long)t;
+    p.trace[(size_t)(blockIdx.x * gridDim.y + blockIdx.y) * 16 + slot] = (long long)t;
   }
 }
 
@@ -163,14 +163,38 @@ template <int BN, int E, bool kSwap>
 struct GemmSmem {
   static constexpr int kStageBytes = kTileR * kBlockK + BN * kBlockK;
   static constexpr int kScaleBytes = ScaleStage<BN, kSwap>::kFloats * 4;
-  static constexpr int kBudget = 200 * 1024 - kScaleBytes;
+  // Narrow column tiles (few tokens) use few registers: two CTAs share an SM, which halves the cost of a
+  // partial last wave and doubles the TMA requests in flight per SM.
+  static constexpr int kCtasPerSm = BN <= 32 ? 2 : 1;
+  static constexpr int kBudget = (kCtasPerSm == 2 ? 100 : 200) * 1024 - kScaleBytes;
   static constexpr int kStages = (kBudget / kStageBytes) > 12 ? 12 : (kBudget / kStageBytes);
   static constexpr int kBarBytes = (2 * kStages + 16) * 8;
   static constexpr int kTotal = kStages * kStageBytes + kBarBytes + kScaleBytes + 64 + 1024;
 };
 
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// Largest split * ceil(chunks / split) over the allowed split factors (1..8).
+constexpr int max_reduction_chunks(int chunks) {
+  int worst = chunks;
+  for (int split = 2; split <= 8; ++split) {
+    const int used = split * ((chunks + split - 1) / split);
+    if (used > worst) worst = used;
+  }
+  return worst;
+}
+
 template <int BN, int E, bool kSwap>
-__global__ void __launch_bounds__((E + 2) * 32, 1)
+__global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
     fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_c,
                     const GemmParams p) {
   using S = GemmSmem<BN, E, kSwap>;
@@ -179,10 +203,14 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
   constexpr int kCols = E == 8 ? BN / 2 : BN;  // accumulator columns owned by one epilogue warp
   // Accumulator ring in TMEM: as many BN-column buffers as fit (at most 8), so the MMA issuer can run
   // several K blocks ahead of the promotion.
-  constexpr int kAcc = 512 / BN > 8 ? 8 : 512 / BN;
+  constexpr int kAcc = (512 / S::kCtasPerSm) / BN > 8 ? 8 : (512 / S::kCtasPerSm) / BN;
   constexpr uint32_t kTmemCols = kAcc * BN < 32 ? 32 : kAcc * BN;
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
   static_assert(kCols % 16 == 0, "column slice must be a multiple of 16");
+  // The stage ring doubles as the landing zone of the cluster reduction: split slots of ceil(BN/8/split)
+  // 8-column chunks each, at most (BN/8 + 7) chunks in total.
+  static_assert(kStages * S::kStageBytes >= max_reduction_chunks(BN / 8) * 8 * kTileR * 4,
+                "stage ring too small for the reduction");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -197,10 +225,10 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb_total = (p.k + kBlockK - 1) / kBlockK;
   const int tiles_r = (p.rows_r + kTileR - 1) / kTileR;
-  const int tiles_c = (p.rows_c + BN - 1) / BN;
-  const long long iters = (long long)tiles_r * tiles_c * kb_total;
-  const int G = gridDim.x;
-  const long long it_begin = iters * blockIdx.x / G, it_end = iters * (blockIdx.x + 1) / G;
+  const int split = gridDim.y, rank = blockIdx.y, tile = blockIdx.x;  // cluster = (1, split, 1)
+  const int tr = tile % tiles_r, tc = tile / tiles_r;
+  const int kb_first = (int)((long long)kb_total * rank / split);
+  const int kb_last = (int)((long long)kb_total * (rank + 1) / split);  // exclusive
 
   if (threadIdx.x == 0) trace_stamp(p, 0);
   if (threadIdx.x == 0) {
@@ -226,14 +254,19 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) trace_stamp(p, 1);
 
+  // Epilogue state that outlives the role branch (the reduction below needs it).
+  constexpr int kEpiThreads = E * 32;
+  const int quad = warp & 3, half = E == 8 ? (warp >> 2) & 1 : 0;
+  const int row_in_tile = quad * 32 + lane;
+  const int col0 = half * kCols;
+  float acc[kCols];
+
   if (warp == E) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
       const uint64_t stream_policy = l2_evict_first_policy();
       uint32_t n = 0;
-      for (long long it = it_begin; it < it_end; ++it, ++n) {
-        const int tile = (int)(it / kb_total), kb = (int)(it % kb_total);
-        const int tr = tile % tiles_r, tc = tile / tiles_r;
+      for (int kb = kb_first; kb < kb_last; ++kb, ++n) {
         const int s = n % kStages;
         if (!mbar_wait_bounded(&empty_bar[s], ((n / kStages) & 1u) ^ 1u)) {
           raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
@@ -255,7 +288,7 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc_f8(BN);
       uint32_t n = 0;
-      for (long long it = it_begin; it < it_end; ++it, ++n) {
+      for (int kb = kb_first; kb < kb_last; ++kb, ++n) {
         const int s = n % kStages, b = n % kAcc;
         if (!mbar_wait_bounded(&full_bar[s], (n / kStages) & 1u) ||
             !mbar_wait_bounded(&tmem_empty[b], ((n / kAcc) & 1u) ^ 1u)) {
@@ -278,164 +311,212 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
       trace_stamp(p, 5);
     }
   } else {
-    // ---------------- Epilogue warps ----------------
-    const int quad = warp & 3, half = E == 8 ? warp >> 2 : 0;
-    const int row_in_tile = quad * 32 + lane;
-    const int col0 = half * kCols;
+    // ---------------- Epilogue warps: promote every K block with its scales ----------------
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const int epi_threads = E * 32;
     const int epi_tid = threadIdx.x;  // epilogue warps are warps 0..E-1
-    float acc[kCols];
+    const int wblk = tr;              // swapped mode: the tile's 128 weight rows are one scale block
     uint32_t n = 0;
     bool ok = true;
-    long long it = it_begin;
-    while (it < it_end && ok) {
-      const int tile = (int)(it / kb_total), kb_first = (int)(it % kb_total);
-      const int tr = tile % tiles_r, tc = tile / tiles_r;
-      const long long tile_it0 = (long long)tile * kb_total;
-      const long long seg_end = tile_it0 + kb_total < it_end ? tile_it0 + kb_total : it_end;
-      const int kb_last = (int)(seg_end - tile_it0);  // exclusive
 #pragma unroll
-      for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
-
-      // Logical coordinates of this thread's accumulator row.
-      const int r_glob = tr * kTileR + row_in_tile;  // token (normal) or weight row (swapped)
-      const int wblk = kSwap ? tr : (tc * BN + col0) / 128;  // weight scale block of this warp's slice
-
-      for (int kb0 = kb_first; kb0 < kb_last && ok; kb0 += SS::kChunkKb) {
-        const int kc = kb_last - kb0 < SS::kChunkKb ? kb_last - kb0 : SS::kChunkKb;
-        // Stage this chunk's scales (all loads in flight together).
-        epi_bar_sync(epi_threads);  // the previous chunk's readers are done
-        float* s_w = sscale + SS::kChunkKb * SS::kWidth;
-        if (kSwap) {
-          // Products a_scale[token] * w_scale, one per (K block, column).
-          for (int i = epi_tid; i < kc * BN; i += epi_threads) {
-            const int kk = i / BN, tok = tc * BN + i % BN;
-            const float ws = p.w_scale[(long long)wblk * p.w_scale_ld + kb0 + kk];
-            sscale[i] = tok < p.m ? p.a_scale[(long long)(kb0 + kk) * p.a_scale_ld + tok] * ws : 0.f;
-          }
-        } else {
-          for (int i = epi_tid; i < kc * kTileR; i += epi_threads) {
-            const int kk = i / kTileR, tok = tr * kTileR + i % kTileR;
-            sscale[i] = tok < p.m ? p.a_scale[(long long)(kb0 + kk) * p.a_scale_ld + tok] : 0.f;
-          }
-          for (int i = epi_tid; i < kc * SS::kWBlocks; i += epi_threads) {
-            const int kk = i / SS::kWBlocks, blk = (tc * BN) / 128 + i % SS::kWBlocks;
-            s_w[i] = blk * 128 < p.n ? p.w_scale[(long long)blk * p.w_scale_ld + kb0 + kk] : 0.f;
-          }
+    for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+    for (int kb0 = kb_first; kb0 < kb_last && ok; kb0 += SS::kChunkKb) {
+      const int kc = kb_last - kb0 < SS::kChunkKb ? kb_last - kb0 : SS::kChunkKb;
+      // Stage this chunk's scales (all loads in flight together).
+      epi_bar_sync(kEpiThreads);  // the previous chunk's readers are done
+      float* s_w = sscale + SS::kChunkKb * SS::kWidth;
+      if (kSwap) {
+        // Products a_scale[token] * w_scale, one per (K block, column).
+        for (int i = epi_tid; i < kc * BN; i += kEpiThreads) {
+          const int kk = i / BN, tok = tc * BN + i % BN;
+          const float ws = p.w_scale[(long long)wblk * p.w_scale_ld + kb0 + kk];
+          sscale[i] = tok < p.m ? p.a_scale[(long long)(kb0 + kk) * p.a_scale_ld + tok] * ws : 0.f;
         }
-        epi_bar_sync(epi_threads);
-        if (epi_tid == 0 && n == 0) trace_stamp(p, 6);
-        for (int kk = 0; kk < kc; ++kk, ++n) {
-          const int b = n % kAcc;
-          float s_row = 0.f;
-          if (!kSwap) s_row = sscale[kk * kTileR + row_in_tile] * s_w[kk * SS::kWBlocks + (col0 / 128)];
-          const float* s_col = sscale + kk * BN + col0;  // swapped mode: one product per column
-          if (!mbar_wait_bounded(&tmem_full[b], (n / kAcc) & 1u)) {
-            raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          if (epi_tid == 0 && n == 0) trace_stamp(p, 7);
-          const uint32_t taddr = lane_addr + (uint32_t)(b * BN + col0);
-          if constexpr (kCols % 64 == 0) {
-            // Two loads in flight per wait: halves the TMEM round trips per K block.
+      } else {
+        for (int i = epi_tid; i < kc * kTileR; i += kEpiThreads) {
+          const int kk = i / kTileR, tok = tr * kTileR + i % kTileR;
+          sscale[i] = tok < p.m ? p.a_scale[(long long)(kb0 + kk) * p.a_scale_ld + tok] : 0.f;
+        }
+        for (int i = epi_tid; i < kc * SS::kWBlocks; i += kEpiThreads) {
+          const int kk = i / SS::kWBlocks, blk = (tc * BN) / 128 + i % SS::kWBlocks;
+          s_w[i] = blk * 128 < p.n ? p.w_scale[(long long)blk * p.w_scale_ld + kb0 + kk] : 0.f;
+        }
+      }
+      epi_bar_sync(kEpiThreads);
+      if (epi_tid == 0 && n == 0) trace_stamp(p, 6);
+      for (int kk = 0; kk < kc; ++kk, ++n) {
+        const int b = n % kAcc;
+        float s_row = 0.f;
+        if (!kSwap) s_row = sscale[kk * kTileR + row_in_tile] * s_w[kk * SS::kWBlocks + (col0 / 128)];
+        const float* s_col = sscale + kk * BN + col0;  // swapped mode: one product per column
+        if (!mbar_wait_bounded(&tmem_full[b], (n / kAcc) & 1u)) {
+          raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        if (epi_tid == 0 && n == 0) trace_stamp(p, 7);
+        const uint32_t taddr = lane_addr + (uint32_t)(b * BN + col0);
+        if constexpr (kCols % 64 == 0) {
+          // Two loads in flight per wait: halves the TMEM round trips per K block.
 #pragma unroll
-            for (int c = 0; c < kCols; c += 64) {
-              float d0[32], d1[32];
-              tmem_ld32(taddr + c, d0);
-              tmem_ld32(taddr + c + 32, d1);
-              tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(d0[j], kSwap ? s_col[c + j] : s_row, acc[c + j]);
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                acc[c + 32 + j] = fmaf(d1[j], kSwap ? s_col[c + 32 + j] : s_row, acc[c + 32 + j]);
-            }
-          } else if constexpr (kCols % 32 == 0) {
-#pragma unroll
-            for (int c = 0; c < kCols; c += 32) {
-              float d[32];
-              tmem_ld32(taddr + c, d);
-              tmem_ld_wait();
-#pragma unroll
-              for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(d[j], kSwap ? s_col[c + j] : s_row, acc[c + j]);
-            }
-          } else {
-            float d[16];
-            tmem_ld16(taddr, d);
+          for (int c = 0; c < kCols; c += 64) {
+            float d0[32], d1[32];
+            tmem_ld32(taddr + c, d0);
+            tmem_ld32(taddr + c + 32, d1);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[j] = fmaf(d[j], kSwap ? s_col[j] : s_row, acc[j]);
+            for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(d0[j], kSwap ? s_col[c + j] : s_row, acc[c + j]);
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              acc[c + 32 + j] = fmaf(d1[j], kSwap ? s_col[c + 32 + j] : s_row, acc[c + 32 + j]);
           }
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&tmem_empty[b]);
+        } else if constexpr (kCols % 32 == 0) {
+#pragma unroll
+          for (int c = 0; c < kCols; c += 32) {
+            float d[32];
+            tmem_ld32(taddr + c, d);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(d[j], kSwap ? s_col[c + j] : s_row, acc[c + j]);
+          }
+        } else {
+          float d[16];
+          tmem_ld16(taddr, d);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] = fmaf(d[j], kSwap ? s_col[j] : s_row, acc[j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tmem_empty[b]);
+      }
+    }
+    if (epi_tid == 0) trace_stamp(p, 8);
+  }
+
+  // ---------------- output: direct (split == 1) or reduced across the cluster ----------------
+  const int r_glob = tr * kTileR + row_in_tile;  // token (normal) or weight row (swapped)
+  if (split == 1) {
+    if (warp < E) {
+      if (kSwap) {
+        if (r_glob < p.n) {
+#pragma unroll
+          for (int j = 0; j < kCols; ++j) {
+            const int tok = tc * BN + col0 + j;
+            if (tok < p.m) {
+              if (p.out_f16)
+                reinterpret_cast<__half*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2half_rn(acc[j]);
+              else
+                reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2bfloat16_rn(acc[j]);
+            }
+          }
+        }
+      } else if (r_glob < p.m) {
+        const int n0 = tc * BN + col0;
+        uint16_t* yrow = reinterpret_cast<uint16_t*>(p.y) + (long long)r_glob * p.ldy + n0;
+        const bool vec = (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) && (n0 + kCols <= p.n);
+        if (vec) {
+#pragma unroll
+          for (int j = 0; j < kCols; j += 8) {
+            uint32_t w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              w[q] = p.out_f16 ? Mma16816<__half>::pack(acc[j + 2 * q], acc[j + 2 * q + 1])
+                               : Mma16816<__nv_bfloat16>::pack(acc[j + 2 * q], acc[j + 2 * q + 1]);
+            }
+            *reinterpret_cast<uint4*>(yrow + j) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < kCols; ++j) {
+            if (n0 + j < p.n) {
+              if (p.out_f16)
+                reinterpret_cast<__half*>(yrow)[j] = __float2half_rn(acc[j]);
+              else
+                reinterpret_cast<__nv_bfloat16*>(yrow)[j] = __float2bfloat16_rn(acc[j]);
+            }
+          }
         }
       }
-      if (!ok) break;
-
-      // ---- segment done: a whole tile is stored directly; a partial K range goes to the workspace
-      //      and the fix-up kernel sums the contributions of each split tile in a fixed order ----
-      if (epi_tid == 0 && it == it_begin) trace_stamp(p, 8);
-      const bool whole = kb_first == 0 && kb_last == kb_total;
-      const bool do_store = whole;
-      if (!whole) {
-        const int slot = it == it_begin ? 0 : 1;
-        float* ws_tile = p.workspace + ((size_t)blockIdx.x * 2 + slot) * (size_t)(BN * kTileR);
+    }
+  } else {
+    // Every MMA of this CTA has completed (the epilogue consumed the last accumulator), so the stage ring
+    // is free.  Rank d owns the 8-column chunks [d * slice, (d + 1) * slice) of the tile: every CTA pushes
+    // its partial of those columns into slot [its own rank] of the owner's ring (remote shared-memory
+    // stores), the cluster barrier publishes them, and the owner adds the slots in rank order.
+    constexpr int kChunks = BN / 8;
+    const int slice = (kChunks + split - 1) / split;            // chunks per owner
+    const int slice_floats = slice * 8 * kTileR;                 // one slot
+    const uint32_t red_addr = smem_u32(stage_base);
+    cluster_sync_all();  // every CTA of the cluster is done with its own stage ring
+    if (warp < E) {
 #pragma unroll
-        for (int j = 0; j < kCols; ++j) ws_tile[(size_t)(col0 + j) * kTileR + row_in_tile] = acc[j];
-        if (epi_tid == 0 && it == it_begin) trace_stamp(p, 9);
+      for (int j = 0; j < kCols; ++j) {
+        const int col = col0 + j, owner = (col >> 3) / slice;
+        const int local_col = col - owner * slice * 8;
+        const uint32_t local = red_addr + (uint32_t)((rank * slice_floats + local_col * kTileR + row_in_tile) * 4);
+        uint32_t remote;
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)owner));
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(acc[j]) : "memory");
       }
-      if (do_store) {
+    }
+    if (threadIdx.x == 0) trace_stamp(p, 9);
+    cluster_sync_all();
+    if (warp < E) {
+      const float* red = reinterpret_cast<const float*>(stage_base);
+      const int chunk_lo = rank * slice, chunk_hi = (rank + 1) * slice < kChunks ? (rank + 1) * slice : kChunks;
+      for (int ch = chunk_lo + (E == 8 ? (warp >> 2) : 0); ch < chunk_hi; ch += (E == 8 ? 2 : 1)) {
+        float sum[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) sum[j] = 0.f;
+        for (int peer = 0; peer < split; ++peer) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            sum[j] += red[peer * slice_floats + ((ch - chunk_lo) * 8 + j) * kTileR + row_in_tile];
+        }
         if (kSwap) {
-          // acc[j] belongs to token tc*BN + col0 + j, weight row r_glob.
           if (r_glob < p.n) {
 #pragma unroll
-            for (int j = 0; j < kCols; ++j) {
-              const int tok = tc * BN + col0 + j;
+            for (int j = 0; j < 8; ++j) {
+              const int tok = tc * BN + ch * 8 + j;
               if (tok < p.m) {
                 if (p.out_f16)
-                  reinterpret_cast<__half*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2half_rn(acc[j]);
+                  reinterpret_cast<__half*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2half_rn(sum[j]);
                 else
                   reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)tok * p.ldy + r_glob] =
-                      __float2bfloat16_rn(acc[j]);
+                      __float2bfloat16_rn(sum[j]);
               }
             }
           }
         } else if (r_glob < p.m) {
-          const int n0 = tc * BN + col0;
+          const int n0 = tc * BN + ch * 8;
           uint16_t* yrow = reinterpret_cast<uint16_t*>(p.y) + (long long)r_glob * p.ldy + n0;
-          const bool vec = (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) && (n0 + kCols <= p.n);
+          const bool vec = (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) && (n0 + 8 <= p.n);
           if (vec) {
+            uint32_t w[4];
 #pragma unroll
-            for (int j = 0; j < kCols; j += 8) {
-              uint32_t w[4];
-#pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                w[q] = p.out_f16 ? Mma16816<__half>::pack(acc[j + 2 * q], acc[j + 2 * q + 1])
-                                 : Mma16816<__nv_bfloat16>::pack(acc[j + 2 * q], acc[j + 2 * q + 1]);
-              }
-              *reinterpret_cast<uint4*>(yrow + j) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int q = 0; q < 4; ++q) {
+              w[q] = p.out_f16 ? Mma16816<__half>::pack(sum[2 * q], sum[2 * q + 1])
+                               : Mma16816<__nv_bfloat16>::pack(sum[2 * q], sum[2 * q + 1]);
             }
+            *reinterpret_cast<uint4*>(yrow) = make_uint4(w[0], w[1], w[2], w[3]);
           } else {
 #pragma unroll
-            for (int j = 0; j < kCols; ++j) {
+            for (int j = 0; j < 8; ++j) {
               if (n0 + j < p.n) {
                 if (p.out_f16)
-                  reinterpret_cast<__half*>(yrow)[j] = __float2half_rn(acc[j]);
+                  reinterpret_cast<__half*>(yrow)[j] = __float2half_rn(sum[j]);
                 else
-                  reinterpret_cast<__nv_bfloat16*>(yrow)[j] = __float2bfloat16_rn(acc[j]);
+                  reinterpret_cast<__nv_bfloat16*>(yrow)[j] = __float2bfloat16_rn(sum[j]);
               }
             }
           }
         }
       }
-      it = seg_end;
     }
-    if (epi_tid == 0) trace_stamp(p, 11);
+    // No CTA reads a peer after the barrier above, so nothing more is needed before exit.
   }
+  if (threadIdx.x == 0) trace_stamp(p, 11);
 
   tc_fence_before();
   __syncthreads();
@@ -444,65 +525,6 @@ __global__ void __launch_bounds__((E + 2) * 32, 1)
     tmem_dealloc(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0) trace_stamp(p, 12);
-}
-
-// --------------------------------------------------------------------------
-// Fix-up: sums the fp32 partials of every tile whose K range was shared by several CTAs.
-// grid = (tiles, BN / 16); 128 threads = the tile's rows; each block owns 16 columns.
-// The contributors of a tile and their workspace slots follow from the same arithmetic
-// the GEMM kernel uses, so no flags or counters are exchanged.
-// --------------------------------------------------------------------------
-template <int BN, bool kSwap>
-__global__ void __launch_bounds__(kTileR) fp8_gemm_fixup_kernel(const GemmParams p, int G) {
-  const int kb_total = (p.k + kBlockK - 1) / kBlockK;
-  const int tiles_r = (p.rows_r + kTileR - 1) / kTileR;
-  const int tiles_c = (p.rows_c + BN - 1) / BN;
-  const long long iters = (long long)tiles_r * tiles_c * kb_total;
-  const int tile = blockIdx.x, cchunk = blockIdx.y * 16, row = threadIdx.x;
-  const long long t0 = (long long)tile * kb_total, t1 = t0 + kb_total;
-  int c_first = (int)((t0 * G) / iters);
-  while (iters * (c_first + 1) / G <= t0) ++c_first;
-  while (c_first > 0 && iters * c_first / G > t0) --c_first;
-  int c_last = c_first;
-  while (iters * (c_last + 1) / G < t1) ++c_last;
-  if (c_last == c_first) return;  // one CTA had the whole K range and stored the tile itself
-  float acc[16];
-#pragma unroll
-  for (int j = 0; j < 16; ++j) acc[j] = 0.f;
-  for (int c = c_first; c <= c_last; ++c) {
-    const long long r0 = iters * c / G;
-    const int slot = r0 >= t0 ? 0 : 1;  // a segment that opens its CTA's range is slot 0
-    const float* src = p.workspace + ((size_t)c * 2 + slot) * (size_t)(BN * kTileR);
-#pragma unroll
-    for (int j = 0; j < 16; ++j) acc[j] += src[(size_t)(cchunk + j) * kTileR + row];
-  }
-  const int tr = tile % tiles_r, tc = tile / tiles_r;
-  const int r_glob = tr * kTileR + row;
-  if (kSwap) {
-    if (r_glob >= p.n) return;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      const int tok = tc * BN + cchunk + j;
-      if (tok < p.m) {
-        if (p.out_f16)
-          reinterpret_cast<__half*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2half_rn(acc[j]);
-        else
-          reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2bfloat16_rn(acc[j]);
-      }
-    }
-  } else {
-    if (r_glob >= p.m) return;
-    const int n0 = tc * BN + cchunk;
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      if (n0 + j < p.n) {
-        if (p.out_f16)
-          reinterpret_cast<__half*>(p.y)[(long long)r_glob * p.ldy + n0 + j] = __float2half_rn(acc[j]);
-        else
-          reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)r_glob * p.ldy + n0 + j] = __float2bfloat16_rn(acc[j]);
-      }
-    }
-  }
 }
 
 // --------------------------------------------------------------------------
@@ -605,8 +627,30 @@ int operand_map(const void* ptr, long long rows, long long k, long long ld, int 
   return MIE_OK;
 }
 
+// K-split factor for a shape with `tiles` output tiles of `kb_total` K blocks.  Cost model in units of
+// one K block of a 256-column tile: waves * (K blocks per CTA + fixed cost) + the cluster reduction
+// (which grows with the tile width).  Only cluster sizes 1, 2 and 4 are used: 3 and 8 co-schedule badly
+// with one 200 KB CTA per SM (measured), and larger splits leave too little work per CTA.
+int choose_split(long long tiles, int kb_total, int bn, int ctas_per_sm, int max_split) {
+  const int slots = sm_count() * ctas_per_sm;
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 4; s *= 2) {
+    if (s > kb_total || (max_split > 0 && s > max_split)) break;
+    const long long ctas = tiles * s;
+    const double waves = (double)((ctas + slots - 1) / slots);
+    const double cost = waves * ((kb_total + s - 1) / s + 4.0) + (s > 1 ? bn / 32.0 : 0.0);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
 template <int BN, int E, bool kSwap>
-int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& p, int grid, cudaStream_t stream) {
+int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& p, long long tiles, int split,
+                cudaStream_t stream) {
   using S = GemmSmem<BN, E, kSwap>;
   static bool configured[64] = {false};
   int dev = 0;
@@ -616,13 +660,20 @@ int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& 
                                   S::kTotal));
     configured[dev] = true;
   }
-  fp8_gemm_kernel<BN, E, kSwap><<<grid, (E + 2) * 32, S::kTotal, stream>>>(mr, mc, p);
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)tiles, (unsigned)split, 1);
+  config.blockDim = dim3((E + 2) * 32, 1, 1);
+  config.dynamicSmemBytes = S::kTotal;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = (unsigned)split;
+  attr[0].val.clusterDim.z = 1;
+  config.attrs = attr;
+  config.numAttrs = 1;
+  MIE_CUDA(cudaLaunchKernelEx(&config, fp8_gemm_kernel<BN, E, kSwap>, mr, mc, p));
   MIE_LAUNCH_CHECK("fp8_gemm_kernel");
-  const long long tiles = (long long)((p.rows_r + kTileR - 1) / kTileR) * ((p.rows_c + BN - 1) / BN);
-  if (tiles % grid != 0) {  // otherwise every CTA range is a whole number of tiles
-    fp8_gemm_fixup_kernel<BN, kSwap><<<dim3((unsigned)tiles, BN / 16), kTileR, 0, stream>>>(p, grid);
-    MIE_LAUNCH_CHECK("fp8_gemm_fixup_kernel");
-  }
   return MIE_OK;
 }
 
@@ -633,14 +684,6 @@ int swap_bn(int m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
 }  // namespace mie
 
 using namespace mie;
-
-extern "C" int64_t mie_fp8_gemm_workspace_bytes(int32_t m, int32_t n, int32_t k) {
-  (void)n;
-  (void)k;
-  const int bn = m <= 128 ? swap_bn(m) : 256;
-  // Two fp32 partial tiles per persistent CTA.
-  return (long long)sm_count() * 2 * bn * kTileR * 4;
-}
 
 extern "C" int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t ldq, float* scales,
                                 int32_t scale_ld, int32_t m, int32_t k, void* stream) {
@@ -663,11 +706,10 @@ extern "C" int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void*
 
 extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
                             int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy,
-                            int32_t out_dtype, int32_t m, int32_t n, int32_t k, void* workspace,
-                            int64_t workspace_bytes, int32_t grid_limit, int32_t* status, int64_t* trace,
-                            void* stream_) {
+                            int32_t out_dtype, int32_t m, int32_t n, int32_t k, int32_t max_split, int32_t* status,
+                            int64_t* trace, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  MIE_CHECK_ARG(x8 && a_scale && w8 && w_scale && y && workspace, "null pointer");
+  MIE_CHECK_ARG(x8 && a_scale && w8 && w_scale && y, "null pointer");
   MIE_CHECK_ARG(m >= 0 && n >= 1 && k >= 1, "invalid GEMM shape %d x %d x %d", m, n, k);
   MIE_CHECK_ARG(out_dtype == MIE_DTYPE_BF16 || out_dtype == MIE_DTYPE_F16, "output must be bf16 or fp16");
   MIE_CHECK_ARG(ldx % 16 == 0 && ldw % 16 == 0, "operand row strides must be multiples of 16 bytes");
@@ -682,15 +724,8 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
   const long long tiles_r = swap ? (n + kTileR - 1) / kTileR : (m + kTileR - 1) / kTileR;
   const long long tiles_c = swap ? (m + bn - 1) / bn : (n + bn - 1) / bn;
   const long long tiles = tiles_r * tiles_c;
-  const long long iters = tiles * kb;
-  const int sms = sm_count();
-  int grid = (int)(iters < sms ? iters : sms);
-  if (grid_limit > 0 && grid_limit < grid) grid = grid_limit;
-  const long long need = (long long)grid * 2 * bn * kTileR * 4;
-  MIE_CHECK_ARG(tiles <= 0x7fffffff / 2, "too many output tiles (%lld)", tiles);
-  MIE_CHECK_ARG(workspace_bytes >= need, "workspace of %lld bytes is too small (need %lld)",
-                (long long)workspace_bytes, need);
-  MIE_CHECK_ARG((reinterpret_cast<uintptr_t>(workspace) & 255) == 0, "workspace must be 256-byte aligned");
+  MIE_CHECK_ARG(tiles <= 0x7fffffff, "too many output tiles (%lld)", tiles);
+  const int split = choose_split(tiles, kb, bn, bn <= 32 ? 2 : 1, max_split);
 
   GemmParams p;
   p.rows_r = swap ? n : m;
@@ -705,7 +740,6 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
   p.y = y;
   p.ldy = ldy;
   p.out_f16 = out_dtype == MIE_DTYPE_F16;
-  p.workspace = reinterpret_cast<float*>(workspace);
   p.status = status;
   p.trace = reinterpret_cast<long long*>(trace);
 
@@ -714,13 +748,13 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
     if (int rc = operand_map(w8, n, k, ldw, kTileR, &mr)) return rc;
     if (int rc = operand_map(x8, m, k, ldx, bn, &mc)) return rc;
     switch (bn) {
-      case 16: return launch_gemm<16, 4, true>(mr, mc, p, grid, stream);
-      case 32: return launch_gemm<32, 4, true>(mr, mc, p, grid, stream);
-      case 64: return launch_gemm<64, 4, true>(mr, mc, p, grid, stream);
-      default: return launch_gemm<128, 4, true>(mr, mc, p, grid, stream);
+      case 16: return launch_gemm<16, 4, true>(mr, mc, p, tiles, split, stream);
+      case 32: return launch_gemm<32, 4, true>(mr, mc, p, tiles, split, stream);
+      case 64: return launch_gemm<64, 4, true>(mr, mc, p, tiles, split, stream);
+      default: return launch_gemm<128, 4, true>(mr, mc, p, tiles, split, stream);
     }
   }
   if (int rc = operand_map(x8, m, k, ldx, kTileR, &mr)) return rc;
   if (int rc = operand_map(w8, n, k, ldw, bn, &mc)) return rc;
-  return launch_gemm<256, 8, false>(mr, mc, p, grid, stream);
+  return launch_gemm<256, 8, false>(mr, mc, p, tiles, split, stream);
 }

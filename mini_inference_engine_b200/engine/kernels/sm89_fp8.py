@@ -103,25 +103,6 @@ def sm89_available(device: torch.device | str | None = None) -> bool:
     return True
 
 
-_workspaces: dict[int, torch.Tensor] = {}
-
-
-def gemm_workspace(device: torch.device) -> torch.Tensor:
-    """Per-device GEMM workspace (tile counters + stream-K partials), zeroed once.
-
-    Calls on one stream share it safely; concurrent GEMMs on different streams
-    of the same device need workspaces of their own.
-    """
-
-    index = device.index if device.index is not None else torch.cuda.current_device()
-    buffer = _workspaces.get(index)
-    if buffer is None:
-        size = int(_lib.load().mie_fp8_gemm_workspace_bytes(4096, 4096, 4096))
-        buffer = torch.zeros(size, dtype=torch.uint8, device=torch.device("cuda", index))
-        _workspaces[index] = buffer
-    return buffer
-
-
 def _supports_call(input, weight, weight_scale_inv, block_size, activation_scale) -> bool:
     return bool(
         input.is_cuda and weight.is_cuda and weight_scale_inv.is_cuda
@@ -191,20 +172,19 @@ def _gemm_weight(weight: torch.Tensor) -> torch.Tensor:
 
 def launch_fp8_gemm(quantized: torch.Tensor, scales_kmajor: torch.Tensor, weight: torch.Tensor,
                     weight_scale_inv: torch.Tensor, output: torch.Tensor, m: int, k: int,
-                    status: torch.Tensor | None = None, grid_limit: int = 0,
+                    status: torch.Tensor | None = None, max_split: int = 0,
                     trace: torch.Tensor | None = None) -> None:
     """``output[m, n] = fp8 block-scaled product``; thin call into ``mie_fp8_gemm``."""
 
     device = output.device
     w = _gemm_weight(weight)
     scales_w = weight_scale_inv if weight_scale_inv.stride(1) == 1 else weight_scale_inv.contiguous()
-    workspace = gemm_workspace(device)
     word = status if status is not None else _lib.status_word(device)
     _lib.check(_lib.load().mie_fp8_gemm(
         _lib.ptr(quantized), quantized.stride(0), _lib.ptr(scales_kmajor), scales_kmajor.stride(0),
         _lib.ptr(w), w.stride(0), _lib.ptr(scales_w), scales_w.stride(0),
         _lib.ptr(output), output.stride(0), _lib.DTYPE_CODES[output.dtype], m, int(weight.shape[0]), k,
-        _lib.ptr(workspace), workspace.numel(), int(grid_limit), _lib.ptr(word), _lib.ptr(trace),
+        int(max_split), _lib.ptr(word), _lib.ptr(trace),
         _lib.stream_arg(device),
     ))
 
@@ -261,8 +241,8 @@ def sm89_fp8_linear(
 def pretune_sm89_fp8(model: Any, max_tokens: int = MAX_M_BUCKET) -> int:
     """Warm every FP8 shape of ``model`` (engine/kernels/sm89_fp8.py:531-558).
 
-    Nothing is autotuned here; the call only creates the TMA descriptors and
-    the workspace ahead of the first request.  Returns shape/bucket pairs.
+    Nothing is autotuned here; the call only creates the TMA descriptors
+    ahead of the first request.  Returns shape/bucket pairs.
     """
 
     shapes = {

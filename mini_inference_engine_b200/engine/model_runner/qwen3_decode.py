@@ -214,7 +214,6 @@ class Qwen3DecodeRunner:
                                       max_batch * max_context, self.device)
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, DecodeBuffers]] = {}
         self.launches_per_step = 0
-        sm89_fp8.gemm_workspace(self.device)
 
     # -- small helpers ------------------------------------------------------------------------
 
