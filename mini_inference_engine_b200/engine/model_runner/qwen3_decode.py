@@ -184,6 +184,25 @@ class DecodeBuffers:
         return copied
 
 
+def sharded_greedy_tokens(local_logits: torch.Tensor, vocab_start: int, tp_size: int, group=None) -> torch.Tensor:
+    """Greedy token ids from vocabulary-sharded logits ``[batch, vocab / tp]``.
+
+    Every rank contributes its best (value, global index) pair per row; one all-gather later each rank
+    picks the pair with the largest value (lowest rank wins ties, which is also the lowest index).
+    """
+
+    batch = local_logits.shape[0]
+    best_value, best_index = local_logits.float().max(dim=-1)
+    if tp_size == 1:
+        return best_index + vocab_start
+    pair = torch.stack((best_value, (best_index + vocab_start).float()), dim=-1).contiguous()
+    flat = torch.empty(tp_size * batch, 2, dtype=torch.float32, device=local_logits.device)
+    torch.distributed.all_gather_into_tensor(flat, pair, group=group)
+    gathered = flat.view(tp_size, batch, 2)
+    winner = gathered[:, :, 0].argmax(dim=0)
+    return gathered[winner, torch.arange(batch, device=local_logits.device), 1].long()
+
+
 class Qwen3DecodeRunner:
     """Decode steps of a Qwen3-shaped FP8 model over paged KV, eager or as a CUDA graph."""
 
@@ -313,12 +332,7 @@ class Qwen3DecodeRunner:
         if self.tp == 1:
             tokens = logits.argmax(dim=-1)
             return (tokens, logits) if return_logits else tokens
-        best_value, best_index = logits.float().max(dim=-1)
-        pair = torch.stack((best_value, (best_index + self.weights.vocab_start).float()), dim=-1)
-        gathered = torch.empty(self.tp, batch, 2, dtype=torch.float32, device=self.device)
-        torch.distributed.all_gather_into_tensor(gathered, pair, group=self.group)
-        winner = gathered[:, :, 0].argmax(dim=0)
-        return gathered[winner, torch.arange(batch, device=self.device), 1].long()
+        return sharded_greedy_tokens(logits, self.weights.vocab_start, self.tp, self.group)
 
     # -- CUDA graph ------------------------------------------------------------------------------
 
@@ -363,4 +377,4 @@ class Qwen3DecodeRunner:
 
 
 __all__ = ["DecodeBuffers", "LayerWeights", "Qwen3DecodeRunner", "Qwen3Shape", "Qwen3Weights",
-           "quantize_weight_blocks", "rope_table"]
+           "quantize_weight_blocks", "rope_table", "sharded_greedy_tokens"]

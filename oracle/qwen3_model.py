@@ -20,11 +20,15 @@ from . import hot_path
 
 
 def decode_step(weights, key_blocks, value_blocks, input_ids, sequence_lengths, block_tables, *, q_heads, kv_heads,
-                head_dim, eps, theta, return_hidden=False):
+                head_dim, eps, theta, return_hidden=False, all_reduce=None, pick_tokens=None):
     """``weights``: object with ``layers`` (each with qkv/o/gate_up/down e4m3 weights, ``*_scale`` block
     scales and the four norm vectors), ``embedding`` and ``final_norm``, all on the CPU.
     ``key_blocks`` / ``value_blocks``: ``[layers, pages, kv_heads, page, dim]``, updated in place.
-    ``sequence_lengths`` counts the new token.  Returns greedy tokens (and the final hidden rows)."""
+    ``sequence_lengths`` counts the new token.  Returns greedy tokens (and the final hidden rows).
+
+    For a tensor-parallel shard pass the LOCAL head counts, ``all_reduce`` (sums a tensor over the ranks,
+    applied after o_proj and down_proj, the only two exchange points) and ``pick_tokens`` (turns this
+    rank's vocabulary-sharded logits into global greedy tokens)."""
 
     batch = input_ids.shape[0]
     hidden = weights.embedding.index_select(0, input_ids)
@@ -44,12 +48,17 @@ def decode_step(weights, key_blocks, value_blocks, input_ids, sequence_lengths, 
         attended = hot_path.paged_decode_attention(q, key_blocks[index], value_blocks[index], block_tables,
                                                    sequence_lengths, 1.0 / math.sqrt(head_dim))
         attn_out = hot_path.fp8_linear(attended.reshape(batch, q_width), layer.o, layer.o_scale)
+        if all_reduce is not None:
+            attn_out = all_reduce(attn_out)
         normed, residual = hot_path.rms_norm(attn_out, layer.post_norm, eps, residual=residual)
         gate_up = hot_path.fp8_linear(normed, layer.gate_up, layer.gate_up_scale)
         inter = gate_up.shape[-1] // 2
         act = hot_path.silu_mul(gate_up[:, :inter], gate_up[:, inter:])
-        hidden = residual + hot_path.fp8_linear(act, layer.down, layer.down_scale)
+        mlp_out = hot_path.fp8_linear(act, layer.down, layer.down_scale)
+        if all_reduce is not None:
+            mlp_out = all_reduce(mlp_out)
+        hidden = residual + mlp_out
     final = hot_path.rms_norm(hidden, weights.final_norm, eps)
-    logits = final @ weights.embedding.t()
-    tokens = logits.argmax(dim=-1)
+    logits = final @ (weights.lm_head if pick_tokens is not None else weights.embedding).t()
+    tokens = logits.argmax(dim=-1) if pick_tokens is None else pick_tokens(logits)
     return (tokens, final, logits) if return_hidden else tokens

@@ -1,0 +1,122 @@
+"""Head-sharded tensor parallelism, host side, on CPU with gloo (world size 2).
+
+Checks what does not need a GPU: shard layout of the merged projections, the two all-reduce points, and the
+vocabulary-sharded greedy exchange.  Each rank runs the CPU oracle's decode step on its shard; the group's
+tokens must equal the unsharded oracle's.
+"""
+
+from __future__ import annotations
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mini_inference_engine_b200 import workloads
+from mini_inference_engine_b200.engine.model_runner.qwen3_decode import (
+    Qwen3Shape,
+    Qwen3Weights,
+    sharded_greedy_tokens,
+)
+from oracle import qwen3_model
+
+SHAPE = Qwen3Shape(layers=2, hidden=512, q_heads=4, kv_heads=2, head_dim=128, intermediate=1024, vocab=2048)
+
+
+def _free_port() -> int:
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
+def _step(weights, tp, pools, ids, lengths, tables, **kwargs):
+    return qwen3_model.decode_step(weights, pools[0], pools[1], ids, lengths, tables, q_heads=SHAPE.q_heads // tp,
+                                   kv_heads=SHAPE.kv_heads // tp, head_dim=SHAPE.head_dim, eps=SHAPE.rms_eps,
+                                   theta=SHAPE.rope_theta, **kwargs)
+
+
+def _inputs():
+    lengths = torch.tensor([6, 40, 17], dtype=torch.int32)
+    tables = workloads.random_block_tables(lengths, num_pages=12, page=16, seed=3, extra_tokens=4)
+    ids = torch.tensor([5, 900, 2000])
+    generator = torch.Generator().manual_seed(11)
+    keys = torch.randn(SHAPE.layers, 12, SHAPE.kv_heads, 16, SHAPE.head_dim, generator=generator).to(torch.bfloat16)
+    values = torch.randn(SHAPE.layers, 12, SHAPE.kv_heads, 16, SHAPE.head_dim, generator=generator).to(torch.bfloat16)
+    return ids, lengths, tables, keys, values
+
+
+def _worker(rank: int, world: int, port: int, queue) -> None:
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        torch.manual_seed(0)
+        weights = Qwen3Weights(SHAPE, torch.device("cpu"), seed=4, tp_rank=rank, tp_size=world)
+        ids, lengths, tables, keys, values = _inputs()
+        local = SHAPE.kv_heads // world
+        pools = (keys[:, :, rank * local:(rank + 1) * local].contiguous(),
+                 values[:, :, rank * local:(rank + 1) * local].contiguous())
+
+        def all_reduce(tensor):
+            summed = tensor.float()
+            dist.all_reduce(summed)
+            return summed.to(tensor.dtype)
+
+        tokens = _step(weights, world, pools, ids, lengths, tables, all_reduce=all_reduce,
+                       pick_tokens=lambda logits: sharded_greedy_tokens(logits, weights.vocab_start, world))
+        queue.put((rank, tokens.tolist()))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_oracle_step_matches_single_rank():
+    ids, lengths, tables, keys, values = _inputs()
+    full = Qwen3Weights(SHAPE, torch.device("cpu"), seed=4)
+    expected, _, logits = _step(full, 1, (keys.clone(), values.clone()), ids, lengths, tables, return_hidden=True)
+    top2 = logits.float().topk(2, dim=-1).values
+    clear = (top2[:, 0] - top2[:, 1]) > top2[:, 0].abs() * 2.0 ** -6
+
+    context = mp.get_context("spawn")
+    queue = context.Queue()
+    port = _free_port()
+    workers = [context.Process(target=_worker, args=(rank, 2, port, queue)) for rank in range(2)]
+    for worker in workers:
+        worker.start()
+    results = dict(queue.get(timeout=180) for _ in workers)
+    for worker in workers:
+        worker.join(timeout=60)
+        assert worker.exitcode == 0
+    assert results[0] == results[1]  # both ranks agree on the sampled tokens
+    for row in range(3):
+        if clear[row]:  # activation groups align with the shard boundaries, so only fp32 summation order differs
+            assert results[0][row] == int(expected[row])
+
+
+def test_shards_are_slices_of_the_unsharded_weights():
+    """With 128-aligned shard boundaries the per-shard block quantisation equals slicing the full one."""
+
+    full = Qwen3Weights(SHAPE, torch.device("cpu"), seed=4, layers=1).layers[0]
+    q_rows, kv_rows, inter = SHAPE.q_heads * 128, SHAPE.kv_heads * 128, SHAPE.intermediate
+    for rank in range(2):
+        shard = Qwen3Weights(SHAPE, torch.device("cpu"), seed=4, tp_rank=rank, tp_size=2, layers=1).layers[0]
+        q = slice(rank * q_rows // 2, (rank + 1) * q_rows // 2)
+        k = slice(q_rows + rank * kv_rows // 2, q_rows + (rank + 1) * kv_rows // 2)
+        v = slice(q_rows + kv_rows + rank * kv_rows // 2, q_rows + kv_rows + (rank + 1) * kv_rows // 2)
+        expected_qkv = torch.cat([full.qkv[q], full.qkv[k], full.qkv[v]])
+        assert torch.equal(shard.qkv.view(torch.uint8), expected_qkv.view(torch.uint8))
+        cols = slice(rank * q_rows // 2, (rank + 1) * q_rows // 2)
+        assert torch.equal(shard.o.view(torch.uint8), full.o[:, cols].contiguous().view(torch.uint8))
+        assert torch.equal(shard.o_scale, full.o_scale[:, rank * q_rows // 256:(rank + 1) * q_rows // 256])
+        g = slice(rank * inter // 2, (rank + 1) * inter // 2)
+        u = slice(inter + rank * inter // 2, inter + (rank + 1) * inter // 2)
+        assert torch.equal(shard.gate_up.view(torch.uint8), torch.cat([full.gate_up[g], full.gate_up[u]]).view(torch.uint8))
+        assert torch.equal(shard.down.view(torch.uint8), full.down[:, g].contiguous().view(torch.uint8))
+    with pytest.raises(ValueError, match="tensor-parallel size"):
+        Qwen3Weights(SHAPE, torch.device("cpu"), tp_size=3)
+
+
+def test_sharded_greedy_single_rank_adds_the_offset():
+    logits = torch.tensor([[0.1, 0.9, 0.3], [0.5, 0.2, 0.4]])
+    assert sharded_greedy_tokens(logits, 100, 1).tolist() == [101, 100]
