@@ -47,6 +47,8 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--layers", type=int, default=None, help="debug: fewer layers (invalid as a result)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--watchdog", type=int, default=900,
+                        help="seconds after which every rank dumps its Python stacks and exits (0 = off)")
     return parser.parse_args()
 
 
@@ -205,6 +207,10 @@ def run_reference_arm(args: argparse.Namespace) -> None:
 
 def main() -> None:
     args = parse_args()
+    if args.watchdog > 0:
+        import faulthandler
+
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
     if args.impl == "reference":
         run_reference_arm(args)
         return
@@ -397,7 +403,12 @@ def main() -> None:
             line["invalid"] = "debug run with fewer layers"
         print(json.dumps(line), flush=True)
     if world > 1:
-        torch.distributed.destroy_process_group()
+        # Captured graphs still hold NCCL kernels; tearing the communicator down under them can block, so
+        # leave together and let process exit reclaim everything.
+        torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
