@@ -1,0 +1,130 @@
+"""Single-kernel micro-benchmarks of the hot path (also the small cases profiled with ncu).
+
+    python -m mini_inference_engine_b200.microbench decode --concurrency 64
+    python -m mini_inference_engine_b200.microbench gemm --shape qkv --rows 256
+    python -m mini_inference_engine_b200.microbench prefill --requests 6
+
+Each prints one JSON line with the CUDA-event time per launch (median of the repeats, L2 flushed by a
+256 MiB fill between repeats) and the algorithmic bytes / FLOPs of the launch.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import torch
+
+from . import workloads
+from .engine.kernels import sm89_fp8
+from .engine.kv_cache import triton_flash_prefill_attention, triton_write_packed_kv
+from .engine.kv_cache.triton_paged_attention import decode_scratch, launch_decode_attention
+
+
+def _time(run, repeats: int, device: torch.device) -> float:
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    for _ in range(3):
+        run()
+    torch.cuda.synchronize(device)
+    samples = []
+    for _ in range(repeats):
+        flush.zero_()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        run()
+        end.record()
+        torch.cuda.synchronize(device)
+        samples.append(start.elapsed_time(end))
+    return statistics.median(samples)
+
+
+def decode(args, device) -> dict:
+    lengths = workloads.lognormal_contexts(args.concurrency, seed=args.concurrency)
+    total = int(lengths.sum())
+    pages = sum(-(-int(n) // workloads.PAGE) for n in lengths) + 8
+    tables = workloads.random_block_tables(lengths, num_pages=pages, seed=1).to(device)
+    kv_heads, q_heads = workloads.KV_HEADS // args.tp, workloads.Q_HEADS // args.tp
+    key_blocks = torch.randn(pages, kv_heads, workloads.PAGE, 128, device=device).to(torch.bfloat16)
+    value_blocks = torch.randn(pages, kv_heads, workloads.PAGE, 128, device=device).to(torch.bfloat16)
+    query = torch.randn(args.concurrency, q_heads, 1, 128, device=device).to(torch.bfloat16)
+    out = torch.empty_like(query)
+    lens = lengths.to(torch.int32).to(device)
+    scratch = decode_scratch(args.concurrency, q_heads, kv_heads, 128, total, device)
+
+    def run():
+        launch_decode_attention(query, out, key_blocks, value_blocks, tables, lens, None, scale=128 ** -0.5,
+                                max_total_tokens=total, scratch=scratch, split_policy=args.split_policy)
+
+    ms = _time(run, args.repeats, device)
+    algorithmic = total * 2 * kv_heads * 128 * 2 + 2 * query.numel() * 2
+    return {"kernel": "paged decode attention (plan + decode + merge)", "concurrency": args.concurrency,
+            "total_context_tokens": total, "us_per_launch": ms * 1e3, "algorithmic_bytes": algorithmic,
+            "gb_per_s": algorithmic / ms / 1e6}
+
+
+def gemm(args, device) -> dict:
+    n, k = workloads.GEMM_SHAPES[args.shape]
+    weights = [(torch.randn(n, k, device=device) * 32).clamp(-448, 448).to(torch.float8_e4m3fn)
+               for _ in range(args.copies)]
+    scales = torch.rand((n + 127) // 128, (k + 127) // 128, device=device) * 0.09 + 0.001
+    x = torch.randn(args.rows, k, device=device).to(torch.bfloat16)
+    quantized, a_scales = sm89_fp8.quantize_activation_kmajor(x)
+    out = torch.empty(args.rows, n, dtype=torch.bfloat16, device=device)
+
+    def run_all():
+        for weight in weights:
+            sm89_fp8.launch_fp8_gemm(quantized, a_scales, weight, scales, out, args.rows, k)
+
+    run_all()
+    torch.cuda.synchronize(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        run_all()
+    ms = _time(graph.replay, args.repeats, device) / args.copies
+    flops = 2.0 * args.rows * n * k
+    traffic = n * k + args.rows * k + 2 * args.rows * n
+    return {"kernel": "fp8 block-scaled gemm", "shape": args.shape, "m": args.rows, "n": n, "k": k,
+            "us_per_launch": ms * 1e3, "tflops": flops / ms / 1e9, "gb_per_s": traffic / ms / 1e6}
+
+
+def prefill(args, device) -> dict:
+    case = workloads.prefill_case(requests=args.requests, seed=0).to(device)
+    triton_write_packed_kv(case.new_keys, case.new_values, case.token_to_sequence, case.token_positions,
+                           case.block_tables, case.key_blocks, case.value_blocks)
+
+    def run():
+        triton_flash_prefill_attention(case.query, case.key_blocks, case.value_blocks, case.block_tables,
+                                       case.cu_seqlens, case.kv_lens, max_query_len=max(case.chunk_lengths),
+                                       scale=case.scale)
+
+    ms = _time(run, args.repeats, device)
+    flops = sum(4 * workloads.Q_HEADS * 128 * (c * p + c * (c + 1) / 2)
+                for p, c in zip(case.prefix_lengths, case.chunk_lengths))
+    return {"kernel": "chunked prefill attention", "prefixes": case.prefix_lengths, "chunks": case.chunk_lengths,
+            "us_per_launch": ms * 1e3, "tflops": flops / ms / 1e9}
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser(description=__doc__)
+    sub = parser.add_subparsers(dest="command", required=True)
+    p = sub.add_parser("decode")
+    p.add_argument("--concurrency", type=int, default=64)
+    p.add_argument("--tp", type=int, default=1)
+    p.add_argument("--split-policy", type=int, default=1)
+    p = sub.add_parser("gemm")
+    p.add_argument("--shape", default="qkv", choices=list(workloads.GEMM_SHAPES))
+    p.add_argument("--rows", type=int, default=256)
+    p.add_argument("--copies", type=int, default=4)
+    p = sub.add_parser("prefill")
+    p.add_argument("--requests", type=int, default=6)
+    for name in ("decode", "gemm", "prefill"):
+        sub.choices[name].add_argument("--repeats", type=int, default=9)
+    args = parser.parse_args()
+    device = torch.device("cuda", 0)
+    result = {"decode": decode, "gemm": gemm, "prefill": prefill}[args.command](args, device)
+    print(json.dumps(result))
+
+
+if __name__ == "__main__":
+    main()
