@@ -170,6 +170,39 @@ int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mie_view4_t k
                                int64_t max_total_tokens, void* scratch, int64_t scratch_bytes, int32_t plan_only,
                                int32_t use_plan, int32_t plan_slot, int32_t* status, void* stream);
 
+/*
+ * Has no counterpart in the reference.  The same ragged decode attention as
+ * mie_paged_decode_attention, for hosts that cannot hand it a scratch buffer
+ * because they have nothing to allocate device memory with: a C / Go / Java
+ * binding that only owns the tensors it was given, or a server that assigned
+ * all free HBM to its KV pool at start-up and keeps no allocator around.  The
+ * work plan and the split-KV partials live in a 16 MiB array that is part of
+ * the library image (mie_decode_builtin_scratch_bytes()); every GPU that loads
+ * the library holds that array until the process exits.  The call performs no
+ * device allocation and frees nothing.
+ *
+ * Limit: mie_decode_scratch_bytes(batch, q_heads, kv_heads, head_dim,
+ * max_total_tokens) must not exceed the array (about 64 requests x 4k tokens
+ * at 32 query heads); larger batches are rejected with
+ * MIE_ERR_INVALID_ARGUMENT and a message, nothing is launched.
+ *
+ * The first call on each device looks the array's device address up (with that
+ * device current); make that first call before any stream capture starts.
+ * All calls share the one array and it keeps whatever the previous call left:
+ * each call rebuilds its plan and zeroes its counters first, so stale contents
+ * are harmless, but two calls that run on the GPU at the same time (different
+ * streams, threads or processes' worth of overlap on one device) race on it.
+ * Run them on one stream, or use mie_paged_decode_attention with separate buffers.
+ */
+int64_t mie_decode_builtin_scratch_bytes(void);
+int mie_paged_decode_attention_static(mie_view4_t query, mie_view4_t out, mie_view4_t key_blocks,
+                                      mie_view4_t value_blocks, mie_index_t block_tables,
+                                      mie_index_t sequence_lengths, mie_index_t query_positions /* ptr may be NULL */,
+                                      int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                                      int32_t block_size, int32_t num_blocks, int32_t table_width, int32_t dtype,
+                                      float scale, int32_t split_policy, int64_t max_total_tokens, int32_t* status,
+                                      void* stream);
+
 /* ------------------------------------------------------------------------
  * Chunked-prefill attention
  * ---------------------------------------------------------------------- */

@@ -715,3 +715,62 @@ extern "C" int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mi
   if (dtype == MIE_DTYPE_BF16) return launch_fast<__nv_bfloat16>(p, kmap, vmap, stream);
   return launch_fast<__half>(p, kmap, vmap, stream);
 }
+
+// ---------------------------------------------------------------------------
+// Decode attention with built-in scratch (no allocation anywhere on the path)
+// ---------------------------------------------------------------------------
+namespace mie {
+namespace {
+
+// The work plan and split-KV partials of mie_paged_decode_attention_static live here instead of in a
+// buffer from the caller.  16 MiB per GPU that loads this library, held until the process exits.
+constexpr long long kBuiltinScratchBytes = 16ll << 20;
+static __device__ __align__(256) unsigned char g_builtin_scratch[kBuiltinScratchBytes];
+
+// In host code `g_builtin_scratch` is only a handle for the runtime, not a device address: the address
+// has to be asked for, once per device, while that device is current.
+int builtin_scratch_address(void** out) {
+  static void* cached[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  MIE_CUDA(cudaGetDevice(&dev));
+  MIE_CHECK_ARG(dev >= 0 && dev < 64, "device index %d is outside the supported range", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == nullptr) {
+    void* address = nullptr;
+    MIE_CUDA(cudaGetSymbolAddress(&address, g_builtin_scratch));
+    MIE_CHECK_ARG(address != nullptr, "the built-in decode scratch has no address on device %d", dev);
+    cached[dev] = address;
+  }
+  *out = cached[dev];
+  return MIE_OK;
+}
+
+}  // namespace
+}  // namespace mie
+
+extern "C" int64_t mie_decode_builtin_scratch_bytes(void) { return mie::kBuiltinScratchBytes; }
+
+extern "C" int mie_paged_decode_attention_static(mie_view4_t query, mie_view4_t out, mie_view4_t key_blocks,
+                                                 mie_view4_t value_blocks, mie_index_t block_tables,
+                                                 mie_index_t sequence_lengths, mie_index_t query_positions,
+                                                 int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t head_dim,
+                                                 int32_t block_size, int32_t num_blocks, int32_t table_width,
+                                                 int32_t dtype, float scale, int32_t split_policy,
+                                                 int64_t max_total_tokens, int32_t* status, void* stream) {
+  MIE_CHECK_ARG(batch >= 0 && q_heads >= 1 && kv_heads >= 1 && head_dim >= 1 && max_total_tokens >= 0,
+                "invalid decode shape");
+  const long long needed = mie_decode_scratch_bytes(batch, q_heads, kv_heads, head_dim, max_total_tokens);
+  MIE_CHECK_ARG(needed > 0 && needed <= mie::kBuiltinScratchBytes,
+                "this batch needs %lld bytes of decode scratch but the built-in buffer holds %lld: lower batch / "
+                "max_total_tokens or call mie_paged_decode_attention with a buffer of your own",
+                needed, mie::kBuiltinScratchBytes);
+  void* scratch = nullptr;
+  if (int rc = mie::builtin_scratch_address(&scratch)) return rc;
+  return mie_paged_decode_attention(query, out, key_blocks, value_blocks, block_tables, sequence_lengths,
+                                    query_positions, batch, q_heads, kv_heads, head_dim, block_size, num_blocks,
+                                    table_width, dtype, scale, split_policy, max_total_tokens, scratch,
+                                    mie::kBuiltinScratchBytes, /*plan_only=*/0, /*use_plan=*/0, /*plan_slot=*/0, status,
+                                    stream);
+}
+
