@@ -4,8 +4,8 @@
  * Every entry point takes plain device pointers, sizes and element strides, a
  * CUDA stream handle and (where metadata is read on the device) a pointer to
  * an int32 status word in device memory.  No entry point allocates device
- * memory unless its comment says so, none synchronises the stream, and all of
- * them may be captured into a CUDA graph.
+ * memory unless its comment says so, none synchronises the stream, and the
+ * ones whose scratch comes from the caller may be captured into a CUDA graph.
  *
  * Return value: 0 on success, a negative MIE_ERR_* code when the arguments
  * are rejected on the host (nothing was launched; mie_last_error() holds a
