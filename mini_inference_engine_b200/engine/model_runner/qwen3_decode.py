@@ -334,6 +334,105 @@ class Qwen3DecodeRunner:
             return (tokens, logits) if return_logits else tokens
         return sharded_greedy_tokens(logits, self.weights.vocab_start, self.tp, self.group)
 
+    # -- packed prefill (whole prompts or chunks over a cached prefix) ----------------------------------
+
+    def prefill_forward(self, input_ids: torch.Tensor, token_to_sequence: torch.Tensor,
+                        token_positions: torch.Tensor, block_tables: torch.Tensor, cu_seqlens: torch.Tensor,
+                        kv_lens: torch.Tensor, max_query_len: int, return_logits: bool = False):
+        """Flat ``[tokens]`` forward of packed prompt chunks (reference: engine/model_runner/qwen3_packed.py:29,
+        qwen3_mixed.py:125): K/V of every token are scattered to their pages, attention is causal within a chunk
+        and sees the request's cached prefix, and only each request's last row is projected to logits.
+        Returns the greedy next token of every request ``[requests]``."""
+
+        from ..kv_cache.triton_flash_prefill import triton_flash_prefill_attention
+
+        shape, lib = self.shape, _lib.load()
+        stream = _lib.stream_arg(self.device)
+        tokens = int(input_ids.shape[0])
+        requests = int(kv_lens.shape[0])
+        hd, lq, lkv = shape.head_dim, self.local_q_heads, self.local_kv_heads
+        hidden = self.weights.embedding.index_select(0, input_ids)
+        residual, mlp_out = None, None
+        scale = 1.0 / math.sqrt(hd)
+        for index, layer in enumerate(self.weights.layers):
+            if index == 0:
+                _, _, quantized = self._norm(hidden, layer.input_norm, quantize=True)
+                residual = hidden
+            else:
+                _, residual, quantized = self._norm(mlp_out, layer.input_norm, residual, quantize=True)
+            qkv = self._gemm(quantized, layer.qkv, layer.qkv_scale, tokens, shape.hidden)
+            queries = torch.empty(tokens, lq, hd, dtype=torch.bfloat16, device=self.device)
+            _lib.check(lib.mie_qkv_norm_rope_write(
+                _lib.ptr(qkv), qkv.stride(0), _lib.ptr(layer.q_norm), _lib.ptr(layer.k_norm), _lib.ptr(self.rope),
+                int(self.rope.shape[0]), _lib.index_arg(token_positions), _lib.index_arg(token_to_sequence),
+                _lib.index_arg(block_tables), _lib.ptr(queries), _lib.view4_arg(self.key_blocks[index]),
+                _lib.view4_arg(self.value_blocks[index]), tokens, lq, lkv, shape.page, self.num_pages, requests,
+                int(block_tables.shape[1]), shape.rms_eps, _lib.ptr(self.status), stream))
+            attended = triton_flash_prefill_attention(queries, self.key_blocks[index], self.value_blocks[index],
+                                                      block_tables, cu_seqlens, kv_lens,
+                                                      max_query_len=max_query_len, scale=scale)
+            attn_q = self._quantize(attended.view(tokens, lq * hd))
+            attn_out = self._all_reduce(self._gemm(attn_q, layer.o, layer.o_scale, tokens, lq * hd))
+            _, residual, quantized = self._norm(attn_out, layer.post_norm, residual, quantize=True)
+            gate_up = self._gemm(quantized, layer.gate_up, layer.gate_up_scale, tokens, shape.hidden)
+            inter = self.local_inter
+            act = torch.empty(tokens, inter, dtype=torch.bfloat16, device=self.device)
+            _lib.check(lib.mie_silu_mul(_lib.ptr(gate_up), _lib.ptr(gate_up[:, inter:]), gate_up.stride(0),
+                                        _lib.ptr(act), None, 0, None, 0, tokens, inter, stream))
+            mlp_out = self._all_reduce(self._gemm(self._quantize(act), layer.down, layer.down_scale, tokens, inter))
+        last_rows = (cu_seqlens[1:].long() - 1).clamp_min(0)
+        final, _, _ = self._norm(mlp_out.index_select(0, last_rows), self.weights.final_norm,
+                                 residual.index_select(0, last_rows), quantize=False)
+        logits = torch.matmul(final, self.weights.lm_head.t())
+        picked = sharded_greedy_tokens(logits, self.weights.vocab_start, self.tp, self.group)
+        return (picked, logits) if return_logits else picked
+
+    def generate(self, prompts: list[list[int]], max_new_tokens: int, *, use_graph: bool = True) -> list[list[int]]:
+        """Greedy continuous-batching generation for requests that arrive together (BASELINE configuration 3):
+        one packed whole-prompt prefill, then one decode step per new token (a CUDA graph when ``use_graph``).
+        Pages are handed out in order from the start of the pool."""
+
+        shape, device = self.shape, self.device
+        batch = len(prompts)
+        lengths = [len(p) for p in prompts]
+        needed = [-(-(n + max_new_tokens) // shape.page) for n in lengths]
+        if sum(needed) > self.num_pages:
+            raise ValueError("the KV pool is too small for these requests")
+        width = max(needed)
+        tables = torch.full((batch, width), -1, dtype=torch.int32)
+        cursor = 0
+        for row, pages in enumerate(needed):
+            tables[row, :pages] = torch.arange(cursor, cursor + pages, dtype=torch.int32)
+            cursor += pages
+        tables_dev = tables.to(device)
+        flat = torch.tensor([t for p in prompts for t in p], dtype=torch.int64, device=device)
+        tok2seq = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(lengths)]).to(device)
+        tokpos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths]).to(device)
+        cu = torch.zeros(batch + 1, dtype=torch.int32)
+        cu[1:] = torch.tensor(lengths, dtype=torch.int32).cumsum(0)
+        kv_lens = torch.tensor(lengths, dtype=torch.int32, device=device)
+        next_ids = self.prefill_forward(flat, tok2seq, tokpos, tables_dev, cu.to(device), kv_lens, max(lengths))
+        outputs = [[int(t)] for t in next_ids.tolist()]
+        current = kv_lens.clone()
+        if use_graph and max_new_tokens > 1:
+            buffers = self.capture(batch, width, advance=True)
+            # Capture runs throw-away steps that write position 0 of page 0: restore it from the prompt.
+            self.prefill_forward(flat, tok2seq, tokpos, tables_dev, cu.to(device), kv_lens, max(lengths))
+            buffers.input_ids.copy_(next_ids)
+            buffers.block_tables.copy_(tables_dev)
+            buffers.sequence_lengths.copy_(current + 1)
+        for _ in range(max_new_tokens - 1):
+            if use_graph:
+                self.replay(batch)
+                next_ids = buffers.output_tokens.clone()
+            else:
+                current = current + 1
+                next_ids = self.decode_forward(next_ids, current, tables_dev)
+            for row, token in enumerate(next_ids.tolist()):
+                outputs[row].append(int(token))
+        self.check_status()
+        return outputs
+
     # -- CUDA graph ------------------------------------------------------------------------------
 
     def capture(self, batch: int, table_width: int, *, advance: bool = False) -> DecodeBuffers:

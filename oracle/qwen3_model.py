@@ -62,3 +62,42 @@ def decode_step(weights, key_blocks, value_blocks, input_ids, sequence_lengths, 
     logits = final @ (weights.lm_head if pick_tokens is not None else weights.embedding).t()
     tokens = logits.argmax(dim=-1) if pick_tokens is None else pick_tokens(logits)
     return (tokens, final, logits) if return_hidden else tokens
+
+
+def prefill_step(weights, key_blocks, value_blocks, input_ids, token_to_sequence, token_positions, block_tables,
+                 cu_seqlens, kv_lens, *, q_heads, kv_heads, head_dim, eps, theta, return_hidden=False):
+    """Packed prompt chunks through the model (engine/model_runner/qwen3_packed.py:29-113; attention adapter
+    packed branch engine/kv_cache/qwen3_paged.py:102-189): per layer the new K/V rows are scattered to their
+    pages, attention is causal within a chunk over the whole cached prefix, and each request's last row is
+    projected to logits.  Returns the greedy next token of every request."""
+
+    tokens = input_ids.shape[0]
+    hidden = weights.embedding.index_select(0, input_ids)
+    cos, sin = hot_path.rope_cos_sin(token_positions.view(1, tokens).long(), head_dim, theta)
+    q_width, kv_width = q_heads * head_dim, kv_heads * head_dim
+    for index, layer in enumerate(weights.layers):
+        residual = hidden
+        normed = hot_path.rms_norm(hidden, layer.input_norm, eps)
+        qkv = hot_path.fp8_linear(normed, layer.qkv, layer.qkv_scale)
+        q, k, v = qkv.split((q_width, kv_width, kv_width), dim=-1)
+        q = hot_path.rms_norm(q.reshape(1, tokens, q_heads, head_dim), layer.q_norm, eps).transpose(1, 2)
+        k = hot_path.rms_norm(k.reshape(1, tokens, kv_heads, head_dim), layer.k_norm, eps).transpose(1, 2)
+        v = v.reshape(1, tokens, kv_heads, head_dim).transpose(1, 2)
+        q, k = hot_path.apply_rotary_pos_emb(q, k, cos, sin)
+        hot_path.write_packed_kv(k, v, token_to_sequence, token_positions, block_tables, key_blocks[index],
+                                 value_blocks[index])
+        attended = hot_path.chunked_prefill_attention(q[0].transpose(0, 1).contiguous(), key_blocks[index],
+                                                      value_blocks[index], block_tables, cu_seqlens, kv_lens,
+                                                      1.0 / math.sqrt(head_dim))
+        attn_out = hot_path.fp8_linear(attended.reshape(tokens, q_width), layer.o, layer.o_scale)
+        normed, residual = hot_path.rms_norm(attn_out, layer.post_norm, eps, residual=residual)
+        gate_up = hot_path.fp8_linear(normed, layer.gate_up, layer.gate_up_scale)
+        inter = gate_up.shape[-1] // 2
+        act = hot_path.silu_mul(gate_up[:, :inter], gate_up[:, inter:])
+        hidden = residual + hot_path.fp8_linear(act, layer.down, layer.down_scale)
+    last_rows = cu_seqlens[1:].long() - 1
+    final = hot_path.rms_norm(hidden.index_select(0, last_rows), weights.final_norm, eps)
+    logits = final @ weights.embedding.t()
+    picked = logits.argmax(dim=-1)
+    return (picked, final, logits) if return_hidden else picked
+
