@@ -47,6 +47,8 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--layers", type=int, default=None, help="debug: fewer layers (invalid as a result)")
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--workload", default="config4", choices=["config4", "config3"],
+                        help="config4: ragged decode sweep point (the headline); config3: 8 x (2048 prompt + 128 new)")
     parser.add_argument("--watchdog", type=int, default=900,
                         help="seconds after which every rank dumps its Python stacks and exits (0 = off)")
     return parser.parse_args()
@@ -205,6 +207,41 @@ def run_reference_arm(args: argparse.Namespace) -> None:
 # Our arm
 # ----------------------------------------------------------------------------------------------
 
+def run_config3(args, shape, device, rank, world, group) -> None:
+    """BASELINE configuration 3: 8 requests arrive together, 2048 random prompt ids each, 128 new tokens,
+    greedy, paged KV, CUDA graph for decode.  Output tok/s = new tokens / wall time of the whole generation
+    (the reference's definition, docs/metric_definitions.md:25-27).  One timed generation after one warm-up."""
+
+    from mini_inference_engine_b200.engine.model_runner.qwen3_decode import Qwen3DecodeRunner, Qwen3Weights
+
+    weights = Qwen3Weights(shape, device, seed=0, tp_rank=rank, tp_size=world, layers=args.layers)
+    requests, prompt_len, new_tokens = 8, 2048, 128
+    pages = requests * (-(-(prompt_len + new_tokens) // shape.page)) + 8
+    runner = Qwen3DecodeRunner(weights, num_pages=pages, max_batch=requests, max_context=prompt_len + new_tokens + 8,
+                               process_group=group)
+    generator = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, shape.vocab, (prompt_len,), generator=generator).tolist() for _ in range(requests)]
+    runner.generate(prompts, 4)  # warm-up: tensor maps, cuBLAS, graph capture path
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    outputs = runner.generate(prompts, new_tokens)
+    torch.cuda.synchronize(device)
+    wall = time.perf_counter() - t0
+    if rank == 0:
+        print(json.dumps({
+            "metric": "output tok/s, 8 requests x 2048-token prompts, 128 new tokens (configuration 3)",
+            "value": requests * new_tokens / wall, "unit": "tok/s", "n_gpus": world, "seconds": wall,
+            "higher_is_better": True, "data": "synthetic", "dtype": "fp8_e4m3 GEMM / bf16 KV+activations",
+            "config": {"workload": "config3", "requests": requests, "prompt_tokens": prompt_len,
+                       "new_tokens": new_tokens, "includes": "packed prefill + graph capture + 127 decode steps"},
+            "tokens_first_request": outputs[0][:8],
+        }), flush=True)
+    if world > 1:
+        torch.distributed.barrier()
+        sys.stdout.flush()
+        os._exit(0)
+
+
 def main() -> None:
     args = parse_args()
     if args.watchdog > 0:
@@ -247,6 +284,9 @@ def main() -> None:
         return float(t.item())
 
     shape = Qwen3Shape()
+    if args.workload == "config3":
+        run_config3(args, shape, device, rank, world, group)
+        return
     concurrency, steps, warmup = args.concurrency, args.steps, max(args.warmup, 0)
     weights = Qwen3Weights(shape, device, seed=0, tp_rank=rank, tp_size=tp, layers=args.layers)
     layers = len(weights.layers)
