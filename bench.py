@@ -407,7 +407,7 @@ def main() -> None:
         except (ValueError, KeyError):
             traffic = None
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                "traffic": traffic, "peak_kind": peak_kind, "kernel": "decode_kernel<bf16> + merge_kernel",
+                "traffic": traffic, "peak_kind": peak_kind, "kernel": "decode_kernel<bf16>",
                 "algorithmic_bytes_per_launch": algorithmic, "ms_per_launch": attn_ms}
     runner.check_status()
 

@@ -161,6 +161,10 @@ int64_t mie_decode_scratch_bytes(int32_t batch, int32_t q_heads, int32_t kv_head
  * let a model step build the work plan once (layer 0) and reuse it for the
  * other layers: plan_only=1 builds the plan and returns; use_plan=1 skips the
  * plan kernel and uses slot `plan_slot` (0..63) of the plan's work counters.
+ * out_q8 (optional): additionally writes the output quantised for the o_proj
+ * FP8 GEMM, exactly what mie_fp8_quantize would produce from `out` viewed as
+ * [batch, q_heads * head_dim]: e4m3 rows of ldq8 bytes and out_scales[head *
+ * out_scale_ld + request] (one 128-column group per head).
  */
 int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mie_view4_t key_blocks,
                                mie_view4_t value_blocks, mie_index_t block_tables, mie_index_t sequence_lengths,
@@ -168,7 +172,8 @@ int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mie_view4_t k
                                int32_t kv_heads, int32_t head_dim, int32_t block_size, int32_t num_blocks,
                                int32_t table_width, int32_t dtype, float scale, int32_t split_policy,
                                int64_t max_total_tokens, void* scratch, int64_t scratch_bytes, int32_t plan_only,
-                               int32_t use_plan, int32_t plan_slot, int32_t* status, void* stream);
+                               int32_t use_plan, int32_t plan_slot, void* out_q8 /* may be NULL */, int64_t ldq8,
+                               float* out_scales, int32_t out_scale_ld, int32_t* status, void* stream);
 
 /*
  * Has no counterpart in the reference.  The same ragged decode attention as

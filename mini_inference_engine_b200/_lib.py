@@ -65,7 +65,7 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "mie_paged_decode_attention": (ctypes.c_int, [View4T, View4T, View4T, View4T, IndexT, IndexT, IndexT, c_int32,
                                                   c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                                   c_float, c_int32, c_int64, c_void_p, c_int64, c_int32, c_int32,
-                                                  c_int32, c_void_p, c_void_p]),
+                                                  c_int32, c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_void_p]),
     "mie_decode_builtin_scratch_bytes": (c_int64, []),
     "mie_paged_decode_attention_static": (ctypes.c_int, [View4T, View4T, View4T, View4T, IndexT, IndexT, IndexT,
                                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,

@@ -10,7 +10,8 @@
 //     compute Q.K^T and P.V for all query heads that share the KV head with
 //     mma.sync, so each K/V byte is read from HBM once per group; softmax is
 //     online in fp32 with quad shuffles;
-//   * a merge kernel combines the chunks of requests that were split.
+//   * a merge kernel (one block per request and KV head, exits at once for unsplit requests) combines
+//     the chunks; both kernels can emit the e4m3 + per-head scale form the o_proj GEMM consumes.
 // Everything else takes a generic one-warp-per-(request, head) kernel.
 //
 // The op is HBM-bound (4 FLOP per KV byte at GQA 4:1), so the MMA shape padding
@@ -36,6 +37,7 @@ constexpr int kPlanThreads = 1024;
 constexpr int kHeaderInts = 128;  // [0]=chunk [1]=seq_chunks [2]=items; [16..79] work counters
 constexpr int kCounterBase = 16;
 constexpr int kCounters = 64;
+constexpr int kMaxGroupMerge = 4;  // query heads per KV head the merge kernel handles in one block
 
 struct View4 {
   char* ptr;
@@ -180,6 +182,11 @@ struct DecodeParams {
   float scale_log2;
   int counter_slot;
   int* status;
+  uint8_t* out_q8;     // optional e4m3 copy of the output for the next FP8 GEMM: [batch][ldq8 bytes]
+  long long ldq8;
+  float* out_scales;   // [q_heads][out_scale_ld]: one scale per (head, request) = per 128 columns
+  int out_scale_ld;
+  int merge_head0;     // first head of the group handled by this merge launch
 };
 
 template <typename T>
@@ -380,17 +387,37 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     // Row sum over the quad, then write the result (final or partial).
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (g < p.group) {
-      const int head = h * p.group + g;
-      if (nchunks == 1) {
-        const float inv = 1.f / fmaxf(l, 1.17549435e-38f);
-        T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)b * p.out.s[0] + (long long)head * p.out.s[1];
+    const bool head_live = g < p.group;
+    const int head = h * p.group + (head_live ? g : 0);
+    if (nchunks == 1) {
+      const float inv = 1.f / fmaxf(l, 1.17549435e-38f);
+      T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)b * p.out.s[0] + (long long)head * p.out.s[1];
+      float amax = 0.f;
 #pragma unroll
-        for (int n = 0; n < 16; ++n) {
-          *reinterpret_cast<uint32_t*>(orow + n * 8 + 2 * t) = Mma16816<T>::pack(o[n][0] * inv, o[n][1] * inv);
+      for (int n = 0; n < 16; ++n) {
+        o[n][0] = round_act<T>(o[n][0] * inv);  // the stored (and quantised) value is the rounded one
+        o[n][1] = round_act<T>(o[n][1] * inv);
+        amax = fmaxf(amax, fmaxf(fabsf(o[n][0]), fabsf(o[n][1])));
+        if (head_live) *reinterpret_cast<uint32_t*>(orow + n * 8 + 2 * t) = Mma16816<T>::pack(o[n][0], o[n][1]);
+      }
+      if (p.out_q8 != nullptr) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float scale = __fdiv_rn(amax, 448.0f), denom = fmaxf(scale, 1e-12f);
+        if (head_live) {
+          uint8_t* qrow = p.out_q8 + (long long)b * p.ldq8 + head * kHeadDim;
+#pragma unroll
+          for (int n = 0; n < 16; ++n) {
+            *reinterpret_cast<__nv_fp8x2_storage_t*>(qrow + n * 8 + 2 * t) = __nv_cvt_float2_to_fp8x2(
+                make_float2(__fdiv_rn(o[n][0], denom), __fdiv_rn(o[n][1], denom)), __NV_SATFINITE, __NV_E4M3);
+          }
+          if (t == 0) p.out_scales[(long long)head * p.out_scale_ld + b] = scale;
         }
-      } else {
-        const long long row = (long long)(p.sc.offsets[b] + ck) * p.q_heads + head;
+      }
+    } else {
+      const long long first_row = (long long)p.sc.offsets[b] * p.q_heads;
+      if (head_live) {
+        const long long row = first_row + (long long)ck * p.q_heads + head;
         float* po = p.sc.part_o + row * kHeadDim;
 #pragma unroll
         for (int n = 0; n < 16; ++n) {
@@ -403,52 +430,95 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
       }
     }
   }
+
+  // Requests with nothing to read (rejected metadata) get zeros.
+  const int warps_total = gridDim.x * kWarps;
+  for (int e = blockIdx.x * kWarps + warp; e < p.batch; e += warps_total) {
+    if (p.sc.offsets[e + 1] != p.sc.offsets[e]) continue;
+    for (int hq = 0; hq < p.q_heads; ++hq) {
+      T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)e * p.out.s[0] + (long long)hq * p.out.s[1];
+      *reinterpret_cast<uint2*>(orow + 4 * lane) = make_uint2(0u, 0u);
+      if (p.out_q8 != nullptr) {
+        *reinterpret_cast<uint32_t*>(p.out_q8 + (long long)e * p.ldq8 + hq * kHeadDim + 4 * lane) = 0u;
+        if (lane == 0) p.out_scales[(long long)hq * p.out_scale_ld + e] = 0.f;
+      }
+    }
+  }
 }
 
-// Merge the chunks of split requests; also zero-fills rows with nothing to read.
-// One block per (request, query head); threads first find the global maximum and the
-// per-chunk weights together, then each thread owns one output dimension.
-template <typename T>
-__global__ void __launch_bounds__(kHeadDim) merge_kernel(DecodeParams p) {
-  constexpr int kMaxStaged = 512;
-  __shared__ float weight_s[kMaxStaged];
-  __shared__ float red[4];
-  const int b = blockIdx.x / p.q_heads, head = blockIdx.x % p.q_heads;
+// Merge of split requests: one block per (request, KV head), exits at once when the request was not
+// split.  Each query head of the group gets W warps that share the request's chunks (W = 8 for small
+// batches, whose requests are cut into many chunks, 2 for large ones); their partial merges
+// are combined through shared memory.  Also emits the e4m3 + per-head scale form for the o_proj GEMM.
+
+template <typename T, int kMergeWarpsPerHead>
+__global__ void __launch_bounds__(kMaxGroupMerge * kMergeWarpsPerHead * 32) merge_kernel(DecodeParams p) {
+  __shared__ float part[kMaxGroupMerge][kMergeWarpsPerHead][2 + kHeadDim];
+  const int b = blockIdx.x / p.kv_heads, h = blockIdx.x % p.kv_heads;
   const int first = p.sc.offsets[b], n = p.sc.offsets[b + 1] - first;
-  if (n == 1) return;
-  const int d = threadIdx.x, lane = d & 31, warp = d >> 5;
-  T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)b * p.out.s[0] + (long long)head * p.out.s[1];
-  if (n == 0) {
-    orow[d] = from_float<T>(0.f);
-    return;
-  }
-  const float* pm = p.sc.part_m + (long long)first * p.q_heads + head;
-  const float* pl = p.sc.part_l + (long long)first * p.q_heads + head;
-  float mmax = -INFINITY;
-  for (int i = d; i < n; i += kHeadDim) mmax = fmaxf(mmax, pm[(long long)i * p.q_heads]);
-  mmax = warp_max(mmax);
-  if (lane == 0) red[warp] = mmax;
-  __syncthreads();
-  mmax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-  __syncthreads();
-  float lsum = 0.f;
-  for (int i = d; i < n; i += kHeadDim) {
-    const float w = exp2f(pm[(long long)i * p.q_heads] - mmax);
-    if (i < kMaxStaged) weight_s[i] = w;
-    lsum += pl[(long long)i * p.q_heads] * w;
-  }
-  lsum = warp_sum(lsum);
-  if (lane == 0) red[warp] = lsum;
-  __syncthreads();
-  lsum = (red[0] + red[1]) + (red[2] + red[3]);
-  const float* po = p.sc.part_o + ((long long)first * p.q_heads + head) * kHeadDim + d;
-  const long long stride = (long long)p.q_heads * kHeadDim;
-  float acc = 0.f;
-  const int staged = n < kMaxStaged ? n : kMaxStaged;
+  if (n <= 1) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gh = warp / kMergeWarpsPerHead, sub = warp % kMergeWarpsPerHead;
+  const int head = h * p.group + p.merge_head0 + gh;
+  const long long row0 = (long long)first * p.q_heads + head;
+  const long long stride = p.q_heads;
+  float big = -INFINITY, lsum = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll 8
-  for (int i = 0; i < staged; ++i) acc += po[i * stride] * weight_s[i];
-  for (int i = staged; i < n; ++i) acc += po[i * stride] * exp2f(pm[(long long)i * p.q_heads] - mmax);
-  orow[d] = from_float<T>(acc / fmaxf(lsum, 1.17549435e-38f));
+  for (int i = sub; i < n; i += kMergeWarpsPerHead) {
+    const long long row = row0 + i * stride;
+    const float mi = p.sc.part_m[row], li = p.sc.part_l[row];
+    const float4 oi = reinterpret_cast<const float4*>(p.sc.part_o + row * kHeadDim)[lane];
+    const float mn = fmaxf(big, mi);
+    const float wo = exp2f(big - mn), wi = exp2f(mi - mn);
+    lsum = lsum * wo + li * wi;
+    a0 = a0 * wo + oi.x * wi;
+    a1 = a1 * wo + oi.y * wi;
+    a2 = a2 * wo + oi.z * wi;
+    a3 = a3 * wo + oi.w * wi;
+    big = mn;
+  }
+  float* mine = part[gh][sub];
+  if (lane == 0) {
+    mine[0] = big;
+    mine[1] = lsum;
+  }
+  mine[2 + 4 * lane + 0] = a0;
+  mine[2 + 4 * lane + 1] = a1;
+  mine[2 + 4 * lane + 2] = a2;
+  mine[2 + 4 * lane + 3] = a3;
+  __syncthreads();
+  if (sub != 0) return;
+  big = -INFINITY;
+  for (int w = 0; w < kMergeWarpsPerHead; ++w) big = fmaxf(big, part[gh][w][0]);
+  lsum = a0 = a1 = a2 = a3 = 0.f;
+  for (int w = 0; w < kMergeWarpsPerHead; ++w) {
+    const float mw = part[gh][w][0];
+    if (mw == -INFINITY) continue;  // this warp had no chunk
+    const float wt = exp2f(mw - big);
+    lsum += part[gh][w][1] * wt;
+    a0 += part[gh][w][2 + 4 * lane + 0] * wt;
+    a1 += part[gh][w][2 + 4 * lane + 1] * wt;
+    a2 += part[gh][w][2 + 4 * lane + 2] * wt;
+    a3 += part[gh][w][2 + 4 * lane + 3] * wt;
+  }
+  const float inv = 1.f / fmaxf(lsum, 1.17549435e-38f);
+  a0 = round_act<T>(a0 * inv);
+  a1 = round_act<T>(a1 * inv);
+  a2 = round_act<T>(a2 * inv);
+  a3 = round_act<T>(a3 * inv);
+  T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)b * p.out.s[0] + (long long)head * p.out.s[1];
+  *reinterpret_cast<uint2*>(orow + 4 * lane) = make_uint2(Mma16816<T>::pack(a0, a1), Mma16816<T>::pack(a2, a3));
+  if (p.out_q8 != nullptr) {
+    const float amax = warp_max(fmaxf(fmaxf(fabsf(a0), fabsf(a1)), fmaxf(fabsf(a2), fabsf(a3))));
+    const float scale = __fdiv_rn(amax, 448.0f), denom = fmaxf(scale, 1e-12f);
+    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+        make_float2(__fdiv_rn(a0, denom), __fdiv_rn(a1, denom)), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+        make_float2(__fdiv_rn(a2, denom), __fdiv_rn(a3, denom)), __NV_SATFINITE, __NV_E4M3);
+    *reinterpret_cast<uint32_t*>(p.out_q8 + (long long)b * p.ldq8 + head * kHeadDim + 4 * lane) =
+        (uint32_t)lo | ((uint32_t)hi << 16);
+    if (lane == 0) p.out_scales[(long long)head * p.out_scale_ld + b] = scale;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -574,7 +644,10 @@ namespace {
 constexpr size_t kDecodeSmem = (size_t)kWarps * kStages * kStageBytes + kWarps * kStages * 8 +
                                (size_t)kWarps * kPidBatch * 4 + 1024;
 
-long long fixed_scratch_bytes(int batch) { return kHeaderInts * 4 + align_up((long long)(batch + 1) * 4, 256); }
+long long fixed_scratch_bytes(int batch, int kv_heads) {
+  (void)kv_heads;
+  return kHeaderInts * 4 + align_up((long long)(batch + 1) * 4, 256);
+}
 long long per_chunk_bytes(int q_heads, int head_dim) { return 8 + (long long)q_heads * (head_dim + 2) * 4; }
 
 int target_seq_chunks(int kv_heads) {
@@ -582,12 +655,12 @@ int target_seq_chunks(int kv_heads) {
   return (items + kv_heads - 1) / kv_heads;
 }
 
-Scratch carve(void* scratch, long long bytes, int batch, int q_heads, int head_dim) {
+Scratch carve(void* scratch, long long bytes, int batch, int q_heads, int kv_heads, int head_dim) {
   Scratch s;
   char* base = reinterpret_cast<char*>(scratch);
   s.header = reinterpret_cast<int*>(base);
   s.offsets = reinterpret_cast<int*>(base + kHeaderInts * 4);
-  long long off = fixed_scratch_bytes(batch);
+  long long off = fixed_scratch_bytes(batch, kv_heads);
   const long long avail = bytes - off - 1024;
   long long cap = avail / per_chunk_bytes(q_heads, head_dim);
   if (cap > 0x3fffffff) cap = 0x3fffffff;
@@ -615,8 +688,17 @@ int launch_fast(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMa
   }
   decode_kernel<T><<<sm_count(), kWarps * 32, kDecodeSmem, stream>>>(kmap, vmap, p);
   MIE_LAUNCH_CHECK("decode_kernel");
-  merge_kernel<T><<<p.batch * p.q_heads, kHeadDim, 0, stream>>>(p);
-  MIE_LAUNCH_CHECK("merge_kernel");
+  // Groups wider than kMaxGroupMerge take several passes of head sub-groups.
+  for (int g0 = 0; g0 < p.group; g0 += kMaxGroupMerge) {
+    DecodeParams q = p;
+    q.merge_head0 = g0;
+    const int heads = p.group - g0 < kMaxGroupMerge ? p.group - g0 : kMaxGroupMerge;
+    if (p.batch >= 128)
+      merge_kernel<T, 2><<<p.batch * p.kv_heads, heads * 2 * 32, 0, stream>>>(q);
+    else
+      merge_kernel<T, 8><<<p.batch * p.kv_heads, heads * 8 * 32, 0, stream>>>(q);
+    MIE_LAUNCH_CHECK("merge_kernel");
+  }
   return MIE_OK;
 }
 
@@ -647,7 +729,7 @@ extern "C" int64_t mie_decode_scratch_bytes(int32_t batch, int32_t q_heads, int3
   long long aimed = target_seq_chunks(kv_heads);
   if (max_total_tokens / kMinChunk + 1 < aimed) aimed = max_total_tokens / kMinChunk + 1;
   const long long cap = (long long)batch + aimed + max_total_tokens / kMaxChunk + 2;
-  return fixed_scratch_bytes(batch) + cap * per_chunk_bytes(q_heads, head_dim) + 8 * 256 + 1024;
+  return fixed_scratch_bytes(batch, kv_heads) + cap * per_chunk_bytes(q_heads, head_dim) + 8 * 256 + 1024;
 }
 
 extern "C" int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mie_view4_t key_blocks,
@@ -657,7 +739,8 @@ extern "C" int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mi
                                           int32_t num_blocks, int32_t table_width, int32_t dtype, float scale,
                                           int32_t split_policy, int64_t max_total_tokens, void* scratch,
                                           int64_t scratch_bytes, int32_t plan_only, int32_t use_plan,
-                                          int32_t plan_slot, int32_t* status, void* stream_) {
+                                          int32_t plan_slot, void* out_q8, int64_t ldq8, float* out_scales,
+                                          int32_t out_scale_ld, int32_t* status, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MIE_CHECK_ARG(batch >= 0 && q_heads >= 1 && kv_heads >= 1 && q_heads % kv_heads == 0,
                 "query heads (%d) must be a positive multiple of KV heads (%d)", q_heads, kv_heads);
@@ -674,14 +757,18 @@ extern "C" int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mi
   if (batch == 0) return MIE_OK;
 
   const int group = q_heads / kv_heads;
-  const bool fast = dtype != MIE_DTYPE_F32 && group <= 8 && pages_fit_tma(key_blocks, head_dim, block_size) &&
+  const bool fast = dtype != MIE_DTYPE_F32 && group <= 8 && kv_heads <= 64 && pages_fit_tma(key_blocks, head_dim, block_size) &&
                     pages_fit_tma(value_blocks, head_dim, block_size) && query.stride[3] == 1 &&
                     out.stride[3] == 1 && query.stride[0] % 2 == 0 && query.stride[1] % 2 == 0 &&
                     out.stride[0] % 2 == 0 && out.stride[1] % 2 == 0 &&
                     (reinterpret_cast<uintptr_t>(query.ptr) & 3) == 0 &&
                     (reinterpret_cast<uintptr_t>(out.ptr) & 3) == 0 && scratch != nullptr;
+  MIE_CHECK_ARG(out_q8 == nullptr || (out_scales != nullptr && out_scale_ld >= batch &&
+                                      ldq8 >= (long long)q_heads * head_dim && head_dim == kHeadDim),
+                "the quantised output needs scale storage, a row stride >= q_heads * head_dim and head_dim 128");
   if (!fast) {
     MIE_CHECK_ARG(!plan_only && !use_plan, "work plans exist only for the TMA decode path");
+    MIE_CHECK_ARG(out_q8 == nullptr, "the quantised output exists only on the TMA decode path");
     if (dtype == MIE_DTYPE_BF16)
       return launch_generic<__nv_bfloat16>(query, out, key_blocks, value_blocks, block_tables, sequence_lengths,
                                            query_positions, batch, q_heads, kv_heads, head_dim, block_size,
@@ -696,12 +783,13 @@ extern "C" int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mi
   }
 
   MIE_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 255) == 0, "scratch must be 256-byte aligned");
-  Scratch sc = carve(scratch, scratch_bytes, batch, q_heads, head_dim);
+  Scratch sc = carve(scratch, scratch_bytes, batch, q_heads, kv_heads, head_dim);
   MIE_CHECK_ARG(sc.cap > batch, "scratch of %lld bytes is too small for batch %d", (long long)scratch_bytes, batch);
 
   DecodeParams p{View4(query), View4(out), IndexView(block_tables), IndexView(sequence_lengths),
                  IndexView(query_positions), sc, batch, q_heads, kv_heads, group, block_size, num_blocks,
-                 table_width, scale * 1.4426950408889634f, plan_slot, status};
+                 table_width, scale * 1.4426950408889634f, plan_slot, status, reinterpret_cast<uint8_t*>(out_q8), ldq8,
+                 out_scales, out_scale_ld, 0};
   if (!use_plan) {
     plan_kernel<<<1, kPlanThreads, 0, stream>>>(p.lengths, p.positions, batch, (long long)table_width * block_size,
                                                 kv_heads, split_policy, target_seq_chunks(kv_heads), sc, status);
@@ -770,7 +858,7 @@ extern "C" int mie_paged_decode_attention_static(mie_view4_t query, mie_view4_t 
   return mie_paged_decode_attention(query, out, key_blocks, value_blocks, block_tables, sequence_lengths,
                                     query_positions, batch, q_heads, kv_heads, head_dim, block_size, num_blocks,
                                     table_width, dtype, scale, split_policy, max_total_tokens, scratch,
-                                    mie::kBuiltinScratchBytes, /*plan_only=*/0, /*use_plan=*/0, /*plan_slot=*/0, status,
-                                    stream);
+                                    mie::kBuiltinScratchBytes, /*plan_only=*/0, /*use_plan=*/0, /*plan_slot=*/0,
+                                    /*out_q8=*/nullptr, 0, /*out_scales=*/nullptr, 0, status, stream);
 }
 

@@ -130,8 +130,10 @@ def launch_decode_attention(
     use_plan: bool = False,
     plan_slot: int = 0,
     status: torch.Tensor | None = None,
+    quantized_out: tuple[torch.Tensor, torch.Tensor] | None = None,
 ) -> None:
-    """Thin call into ``mie_paged_decode_attention``; ``output`` has the query's shape."""
+    """Thin call into ``mie_paged_decode_attention``; ``output`` has the query's shape.  ``quantized_out`` =
+    ``(e4m3 [batch, q_heads * 128], scales [q_heads, batch])`` also receives the output quantised for o_proj."""
 
     batch, q_heads, _, head_dim = (int(v) for v in query.shape)
     num_blocks, kv_heads, block_size, _ = (int(v) for v in key_blocks.shape)
@@ -139,6 +141,7 @@ def launch_decode_attention(
     if scratch is None:
         scratch = decode_scratch(batch, q_heads, kv_heads, head_dim, max_total_tokens, device)
     word = status if status is not None else _lib.status_word(device)
+    q8, q_scales = quantized_out if quantized_out is not None else (None, None)
     _lib.check(_lib.load().mie_paged_decode_attention(
         _lib.view4_arg(query), _lib.view4_arg(output), _lib.view4_arg(key_blocks), _lib.view4_arg(value_blocks),
         _lib.index_arg(block_tables), _lib.index_arg(sequence_lengths), _lib.index_arg(query_positions),
@@ -146,6 +149,7 @@ def launch_decode_attention(
         _lib.DTYPE_CODES[query.dtype], float(scale),
         _split_policy() if split_policy is None else int(split_policy),
         int(max_total_tokens), _lib.ptr(scratch), scratch.numel(), int(plan_only), int(use_plan), int(plan_slot),
+        _lib.ptr(q8), 0 if q8 is None else q8.stride(0), _lib.ptr(q_scales), 0 if q_scales is None else q_scales.stride(0),
         _lib.ptr(word), _lib.stream_arg(device),
     ))
 

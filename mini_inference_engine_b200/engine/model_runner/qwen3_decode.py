@@ -305,11 +305,12 @@ class Qwen3DecodeRunner:
                 _lib.view4_arg(self.value_blocks[index]), batch, lq, lkv, shape.page, self.num_pages, batch,
                 int(block_tables.shape[1]), shape.rms_eps, _lib.ptr(self.status), stream))
             attended = torch.empty_like(queries)
+            attn_q = self._quant_buffers(batch, lq * hd)
             launch_decode_attention(queries, attended, self.key_blocks[index], self.value_blocks[index],
                                     block_tables, sequence_lengths, None, scale=scale,
                                     max_total_tokens=batch * self.max_context, scratch=self.scratch,
-                                    split_policy=1, use_plan=index > 0, plan_slot=index, status=self.status)
-            attn_q = self._quantize(attended.view(batch, lq * hd))
+                                    split_policy=1, use_plan=index > 0, plan_slot=index, status=self.status,
+                                    quantized_out=attn_q)
             attn_out = self._all_reduce(self._gemm(attn_q, layer.o, layer.o_scale, batch, lq * hd))
             _, residual, quantized = self._norm(attn_out, layer.post_norm, residual, quantize=True)
             gate_up = self._gemm(quantized, layer.gate_up, layer.gate_up_scale, batch, shape.hidden)

@@ -58,7 +58,7 @@ def decode(args, device) -> dict:
 
     ms = _time(run, args.repeats, device)
     algorithmic = total * 2 * kv_heads * 128 * 2 + 2 * query.numel() * 2
-    return {"kernel": "paged decode attention (plan + decode + merge)", "concurrency": args.concurrency,
+    return {"kernel": "paged decode attention (plan + decode)", "concurrency": args.concurrency,
             "total_context_tokens": total, "us_per_launch": ms * 1e3, "algorithmic_bytes": algorithmic,
             "gb_per_s": algorithmic / ms / 1e6}
 

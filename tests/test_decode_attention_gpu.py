@@ -220,3 +220,48 @@ def test_bad_page_id_sets_status_and_keeps_the_context(device):
     with pytest.raises(ValueError, match="invalid physical block ID"):
         triton_paged_decode_attention(case.query, case.key_blocks, case.value_blocks, tables,
                                       case.sequence_lengths, scale=case.scale)
+
+
+def test_fused_quantised_output_equals_the_standalone_quantiser(device, status_clean):
+    """The e4m3 + per-head scales written by the attention epilogue (single-chunk and merged rows) are
+    bit-identical to pushing the bf16 output through the activation quantiser."""
+
+    from mini_inference_engine_b200.engine.kernels import sm89_fp8
+
+    lengths = (9, 700, 64, 5000, 2048, 31)
+    case = workloads.decode_case(lengths, seed=13, num_pages=512).to(device)
+    batch = len(lengths)
+    for policy in (0, 1, 64):
+        out = torch.empty_like(case.query)
+        q8 = torch.zeros(batch, 32 * 128, dtype=torch.float8_e4m3fn, device=device)
+        scales = torch.full((32, batch), -1.0, dtype=torch.float32, device=device)
+        launch_decode_attention(case.query, out, case.key_blocks, case.value_blocks, case.block_tables,
+                                case.sequence_lengths, None, scale=case.scale, max_total_tokens=sum(lengths),
+                                split_policy=policy, quantized_out=(q8, scales))
+        q_ref, s_ref = sm89_fp8.quantize_activation_kmajor(out.view(batch, 32 * 128))
+        torch.cuda.synchronize()
+        assert torch.equal(q8.view(torch.uint8), q_ref.view(torch.uint8)), policy
+        assert torch.equal(scales, s_ref), policy
+
+
+def test_plan_reuse_across_layers_leaves_counters_clean(device, status_clean):
+    """One plan, several launches on different pools (as the model step does per layer)."""
+
+    lengths = (3000, 40, 1500)
+    cases = [workloads.decode_case(lengths, seed=20 + i, num_pages=300) for i in range(3)]
+    from mini_inference_engine_b200.engine.kv_cache.triton_paged_attention import decode_scratch
+
+    scratch = decode_scratch(3, 32, 8, 128, sum(lengths), device)
+    dev0 = cases[0].to(device)
+    for layer, case in enumerate(cases):
+        dev = case.to(device)
+        out = torch.empty_like(dev.query)
+        launch_decode_attention(dev.query, out, dev.key_blocks, dev.value_blocks, dev0.block_tables,
+                                dev0.sequence_lengths, None, scale=case.scale, max_total_tokens=sum(lengths),
+                                scratch=scratch, split_policy=64, use_plan=layer > 0, plan_slot=layer)
+        torch.cuda.synchronize()
+        host = workloads.DecodeCase(case.query, case.key_blocks, case.value_blocks, cases[0].block_tables,
+                                    case.sequence_lengths, case.scale)
+        expected = hot_path.paged_decode_attention(host.query, host.key_blocks, host.value_blocks, host.block_tables,
+                                                   host.sequence_lengths, host.scale)
+        assert (out.transpose(1, 2).cpu().float() - expected.float()).abs().max().item() <= ATOL, layer

@@ -93,9 +93,9 @@ def test_launch_count_is_reported(device):
     tables = torch.arange(4, dtype=torch.int32, device=device).view(1, 4)
     runner.decode_forward(torch.tensor([1], device=device), torch.tensor([3], dtype=torch.int32, device=device),
                           tables)
-    # Per layer: 3 norms/glue + quantiser + 4 GEMMs (+ a fix-up each when a tile's K range is shared) + q/k-norm
-    # RoPE write + decode + merge; once per step: the split-KV plan and the final norm.
-    assert 2 * 11 + 2 <= runner.launches_per_step <= 2 * 15 + 2
+    # Per layer: add+RMSNorm(+quant) x2, SiLU*up(+quant), 4 GEMMs, q/k-norm + RoPE + KV write, decode attention
+    # and its merge (o_proj quantisation fused into both); once per step: the split-KV plan and the final norm.
+    assert runner.launches_per_step == 2 * 10 + 2
 
 
 def _check_tokens(got, expected, logits_ref, where):
