@@ -220,9 +220,12 @@ int mie_paged_decode_attention_static(mie_view4_t query, mie_view4_t out, mie_vi
  * [tokens, q_heads, head_dim] (token and head strides in elements, head_dim
  * contiguous); request r owns rows cu_seqlens[r] .. cu_seqlens[r+1] and sees
  * kv_lens[r] keys, query row i at position kv_lens[r] - q_len + i.
- * max_query_len is a host bound that sizes the grid.  head_dim 128, bf16/fp16.
+ * max_query_len is a host bound that sizes the grid; total_tokens is the number
+ * of query rows.  head_dim 128, bf16/fp16.  GQA groups of 1/2/4/8 run the
+ * tcgen05 kernel, other shapes the mma.sync kernel.
  */
-int mie_flash_prefill_attention(const void* query, int64_t q_token_stride, int64_t q_head_stride, void* out,
+int mie_flash_prefill_attention(const void* query, int64_t q_token_stride, int64_t q_head_stride,
+                                int64_t total_tokens, void* out,
                                 int64_t o_token_stride, int64_t o_head_stride, mie_view4_t key_blocks,
                                 mie_view4_t value_blocks, mie_index_t block_tables, mie_index_t cu_seqlens,
                                 mie_index_t kv_lens, int32_t requests, int32_t max_query_len, int32_t q_heads,

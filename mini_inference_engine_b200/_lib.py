@@ -71,7 +71,7 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                                          c_int32, c_int32, c_float, c_int32, c_int64, c_void_p,
                                                          c_void_p]),
-    "mie_flash_prefill_attention": (ctypes.c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, View4T,
+    "mie_flash_prefill_attention": (ctypes.c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_int64, c_int64, View4T,
                                                    View4T, IndexT, IndexT, IndexT, c_int32, c_int32, c_int32,
                                                    c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_float,
                                                    c_void_p, c_void_p]),

@@ -8,6 +8,8 @@
 // 16-token, 128-byte-swizzled boxes as the decode kernel; no multicast) into a 2-stage
 // ring of 64-token tiles; Q.K^T and P.V run on mma.sync bf16/fp16 tensor-core tiles with
 // an fp32 online softmax in registers.  Heaviest query tiles are scheduled first.
+#include <stdlib.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -19,6 +21,13 @@ namespace mie {
 int page_tensor_map(const mie_view4_t& pages, int num_blocks, int kv_heads, int block_size, int dtype,
                     CUtensorMap* out);
 bool pages_fit_tma(const mie_view4_t& v, int head_dim, int block_size);
+// Defined in prefill_attention_umma.cu: the tcgen05 kernel; MIE_ERR_UNSUPPORTED when the shape does not fit it.
+int prefill_attention_umma(const void* query, long long q_st, long long q_sh, long long total_tokens, void* out,
+                           long long o_st, long long o_sh, const mie_view4_t& key_blocks,
+                           const mie_view4_t& value_blocks, const mie_index_t& block_tables,
+                           const mie_index_t& cu_seqlens, const mie_index_t& kv_lens, int requests, int max_query_len,
+                           int q_heads, int kv_heads, int block_size, int num_blocks, int table_width, int dtype,
+                           float scale, int* status, cudaStream_t stream);
 
 namespace {
 
@@ -285,7 +294,8 @@ int launch_prefill(const CUtensorMap& kmap, const CUtensorMap& vmap, const Prefi
 
 using namespace mie;
 
-extern "C" int mie_flash_prefill_attention(const void* query, int64_t q_token_stride, int64_t q_head_stride, void* out,
+extern "C" int mie_flash_prefill_attention(const void* query, int64_t q_token_stride, int64_t q_head_stride,
+                                           int64_t total_tokens, void* out,
                                            int64_t o_token_stride, int64_t o_head_stride, mie_view4_t key_blocks,
                                            mie_view4_t value_blocks, mie_index_t block_tables, mie_index_t cu_seqlens,
                                            mie_index_t kv_lens, int32_t requests, int32_t max_query_len,
@@ -309,6 +319,18 @@ extern "C" int mie_flash_prefill_attention(const void* query, int64_t q_token_st
                     (reinterpret_cast<uintptr_t>(out) & 3) == 0,
                 "query/out rows must be 4-byte aligned");
   if (requests == 0 || max_query_len == 0) return MIE_OK;
+  // The tcgen05 kernel takes every shape it supports; MIE_PREFILL_KERNEL=mma forces the mma.sync kernel.
+  static const bool force_mma = [] {
+    const char* v = getenv("MIE_PREFILL_KERNEL");
+    return v != nullptr && v[0] == 'm';
+  }();
+  if (!force_mma) {
+    const int rc = prefill_attention_umma(query, q_token_stride, q_head_stride, total_tokens, out, o_token_stride,
+                                          o_head_stride, key_blocks, value_blocks, block_tables, cu_seqlens, kv_lens,
+                                          requests, max_query_len, q_heads, kv_heads, block_size, num_blocks,
+                                          table_width, dtype, scale, status, (cudaStream_t)stream);
+    if (rc != MIE_ERR_UNSUPPORTED) return rc;
+  }
   CUtensorMap kmap, vmap;
   if (int rc = page_tensor_map(key_blocks, num_blocks, kv_heads, block_size, dtype, &kmap)) return rc;
   if (int rc = page_tensor_map(value_blocks, num_blocks, kv_heads, block_size, dtype, &vmap)) return rc;

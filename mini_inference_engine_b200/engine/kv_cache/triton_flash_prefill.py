@@ -49,7 +49,7 @@ def triton_flash_prefill_attention(
         return out
     device = query.device
     _lib.check(_lib.load().mie_flash_prefill_attention(
-        _lib.ptr(query), query.stride(0), query.stride(1), _lib.ptr(out), out.stride(0), out.stride(1),
+        _lib.ptr(query), query.stride(0), query.stride(1), tokens, _lib.ptr(out), out.stride(0), out.stride(1),
         _lib.view4_arg(key_blocks), _lib.view4_arg(value_blocks), _lib.index_arg(block_tables),
         _lib.index_arg(cu_seqlens), _lib.index_arg(kv_lens), requests, int(max_query_len), heads, kv_heads,
         head_dim, page, num_blocks, int(block_tables.shape[1]), _lib.DTYPE_CODES[query.dtype], float(scale),
