@@ -6,12 +6,13 @@
 //   S = Q K^T      UMMA 128x128x16 (bf16/fp16, fp32 accumulate) into one of two TMEM buffers;
 //   softmax        128 threads, one query row each, read their S row from TMEM, apply the causal /
 //                  length mask and an exp2 softmax against a running reference maximum, and write
-//                  P (16-bit) into a 128-byte-swizzled shared-memory tile;
-//   O += P V       UMMA 128x128x16 with V as the MN-major B operand, accumulated in TMEM over all tiles.
+//                  P (16-bit, two per column) back into TMEM over the S buffer they just read;
+//   O += P V       UMMA 128x128x16 with P as the TMEM A operand and V as the MN-major shared-memory B
+//                  operand, accumulated in TMEM over all tiles.
 // The reference maximum is only moved when a row's maximum grows by more than 2^8 (then that warp
 // rescales its O rows in TMEM), so O is read from TMEM once, at the end.
-// Warp roles: 4 softmax warps, 1 TMA producer (K/V pages gathered through the block table with 16-token
-// boxes, 128-byte swizzle, no multicast; Q with one 3-D box per 64-dim half), 1 MMA issuer that also owns
+// Warp roles: 4 softmax warps, 1 TMA producer (K/V pages gathered through the block table, one 4 KiB
+// box per 16-token page slab, 128-byte swizzle, no multicast), 1 MMA issuer that also owns
 // the TMEM allocation.  Every wait is bounded and reports MIE_STATUS_WAIT_TIMEOUT.
 #include <mutex>
 #include <type_traits>
@@ -22,8 +23,6 @@
 
 namespace mie {
 
-int page_tensor_map(const mie_view4_t& pages, int num_blocks, int kv_heads, int block_size, int dtype,
-                    CUtensorMap* out);
 
 namespace {
 
@@ -31,22 +30,28 @@ constexpr int kDim = 128;
 constexpr int kRows = 128;                       // query rows per CTA (tokens x group heads)
 constexpr int kKv = 128;                         // K/V tokens per tile
 constexpr int kSub = 16;                         // tokens per TMA box
-constexpr int kHalfTile = kKv * 64 * 2;          // [128 rows][64 elems] 16-bit = 16 KiB
-constexpr int kTile = 2 * kHalfTile;             // 32 KiB: Q, K, V or P tile
-constexpr int kKvStages = 2;
+constexpr int kBoxBytes = kSub * kDim * 2;       // 4 KiB: one box = 16 tokens x 128 dims
+constexpr int kTile = kKv * kDim * 2;            // 32 KiB: one K or V tile
+// Shared-memory layout of a K/V tile (what the 5-D box below writes, 128-byte swizzled):
+//   [token / 8 (16 groups)][dim / 64 (2 halves)][token % 8][64 dims = 128 bytes]
+// so for either operand role an 8-token group is 2048 bytes from the next and the two 64-dim halves of a
+// group are 1024 bytes apart.
+constexpr int kGroupStride = 2048;
+constexpr int kHalfStride = 1024;
+constexpr int kKvStages = 3;                     // K and V each have their own ring of this depth
 constexpr int kSoftmaxWarps = 4;
 constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
 constexpr float kRescaleThreshold = 8.0f;        // log2 units
 
-// Shared-memory map (1024-byte aligned): Q | K[2] | V[2] | P | barriers.
-constexpr int kOffQ = 0;
-constexpr int kOffK = kOffQ + kTile;
+// Shared-memory map (1024-byte aligned): K[3] | V[3] | barriers.
+constexpr int kOffK = 0;
 constexpr int kOffV = kOffK + kKvStages * kTile;
-constexpr int kOffP = kOffV + kKvStages * kTile;
-constexpr int kOffBar = kOffP + kTile;
+constexpr int kOffBar = kOffV + kKvStages * kTile;
 constexpr int kSmemBytes = kOffBar + 256 + 1024;
 
 struct UmmaPrefillParams {
+  const char* query;
+  long long q_st, q_sh;
   char* out;
   long long o_st, o_sh;
   IndexView tables, cu_seqlens, kv_lens;
@@ -55,13 +60,20 @@ struct UmmaPrefillParams {
   int* status;
 };
 
-enum Bar { kQFull = 0, kKvFull = 1, kKvEmpty = 3, kSFull = 5, kSEmpty = 7, kPFull = 9, kPEmpty = 10, kVClean = 11,
-           kNumBars = 12 };
+enum Bar { kQFull = 0, kKFull = 1, kKEmpty = 4, kVFull = 7, kVEmpty = 10, kSFull = 13, kPFull = 15, kPvDone = 17,
+           kVClean = 19, kNumBars = 20 };
+
+// 2^x on the special-function unit; -inf gives +0.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
-    prefill_umma_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
-                        const __grid_constant__ CUtensorMap vmap, const UmmaPrefillParams p, const int q_tiles) {
+    prefill_umma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                        const UmmaPrefillParams p, const int q_tiles) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kOffBar);
@@ -86,18 +98,20 @@ __global__ void __launch_bounds__(kThreads, 1)
   const int n_tiles = (int)(last_key / kKv) + 1;
 
   if (threadIdx.x == 0) {
-    mbar_init(&bars[kQFull], 1);
+    mbar_init(&bars[kQFull], kSoftmaxWarps * 32);
     for (int s = 0; s < kKvStages; ++s) {
-      mbar_init(&bars[kKvFull + s], 1);
-      mbar_init(&bars[kKvEmpty + s], 1);
-      mbar_init(&bars[kSFull + s], 1);
-      mbar_init(&bars[kSEmpty + s], kSoftmaxWarps * 32);
+      mbar_init(&bars[kKFull + s], 1);
+      mbar_init(&bars[kKEmpty + s], 1);
+      mbar_init(&bars[kVFull + s], 1);
+      mbar_init(&bars[kVEmpty + s], 1);
     }
-    mbar_init(&bars[kPFull], kSoftmaxWarps * 32);
-    mbar_init(&bars[kPEmpty], 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&bars[kSFull + b], 1);
+      mbar_init(&bars[kPFull + b], kSoftmaxWarps * 32);
+      mbar_init(&bars[kPvDone + b], 1);
+    }
     mbar_init(&bars[kVClean], 1);
     mbar_fence_init();
-    tma_prefetch_desc(&qmap);
     tma_prefetch_desc(&kmap);
     tma_prefetch_desc(&vmap);
   }
@@ -109,21 +123,18 @@ __global__ void __launch_bounds__(kThreads, 1)
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s = tmem_base;            // two S buffers: columns [0,128) and [128,256)
+  const uint32_t tmem_s = tmem_base;            // two S buffers: columns [0,128) and [128,256); P(j) is
+                                                // written over the first 64 columns of S(j)
   const uint32_t tmem_o = tmem_base + 256;      // O: columns [256,384)
+  const uint32_t tmem_q = tmem_base + 384;      // Q (16-bit, two per column): columns [384,448)
 
   if (warp == kSoftmaxWarps) {
     // ---------------- TMA producer (+ V tail sanitiser) ----------------
     const uint64_t policy = l2_evict_first_policy();
-    if (lane == 0) {
-      mbar_expect_tx(&bars[kQFull], kTile);
-      tma_load_3d(smem + kOffQ, &qmap, &bars[kQFull], 0, kvh * p.group, (int)(q_begin + i0));
-      tma_load_3d(smem + kOffQ + kHalfTile, &qmap, &bars[kQFull], 64, kvh * p.group, (int)(q_begin + i0));
-    }
-    for (int j = 0; j < n_tiles; ++j) {
+    // One 128-token K or V tile = eight 16-token boxes per 64-dim half.  Lanes 0..7 each own one box row,
+    // so the eight block-table lookups (dependent global loads) run in parallel.
+    auto load_tile = [&](const CUtensorMap* map, int off_base, int full0, int empty0, int j) -> bool {
       const int s = j % kKvStages;
-      // Lanes 0..7 each own one 16-token box row of the tile: the eight block-table lookups (dependent
-      // global loads) run in parallel instead of back to back.
       long long pid = 0;
       int tok_in_page = 0;
       if (lane < kKv / kSub) {
@@ -139,41 +150,45 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
       bool ok = true;
       if (lane == 0) {
-        ok = mbar_wait_bounded(&bars[kKvEmpty + s], ((j / kKvStages) & 1u) ^ 1u);
+        ok = mbar_wait_bounded(&bars[empty0 + s], ((j / kKvStages) & 1u) ^ 1u);
         if (ok)
-          mbar_expect_tx(&bars[kKvFull + s], 2 * kTile);
+          mbar_expect_tx(&bars[full0 + s], kTile);
         else
           raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (ok && lane < kKv / kSub) {
-        // Boxes past the last needed key still land (page 0) so a stage always receives the same byte
+        // One 4 KiB box per lane.  Boxes past the last needed key still land (page 0) so a stage always receives the same byte
         // count; their scores are masked and their V rows are zeroed below.
-        uint8_t* kdst = smem + kOffK + s * kTile;
-        uint8_t* vdst = smem + kOffV + s * kTile;
-        const int off = lane * kSub * 128;  // 16 rows of 128 bytes
-        tma_load_4d_hint(kdst + off, &kmap, &bars[kKvFull + s], 0, tok_in_page, kvh, (int)pid, policy);
-        tma_load_4d_hint(kdst + kHalfTile + off, &kmap, &bars[kKvFull + s], 64, tok_in_page, kvh, (int)pid, policy);
-        tma_load_4d_hint(vdst + off, &vmap, &bars[kKvFull + s], 0, tok_in_page, kvh, (int)pid, policy);
-        tma_load_4d_hint(vdst + kHalfTile + off, &vmap, &bars[kKvFull + s], 64, tok_in_page, kvh, (int)pid, policy);
+        uint8_t* dst = smem + off_base + s * kTile + lane * kBoxBytes;
+        tma_load_5d_hint(dst, map, &bars[full0 + s], 0, 0, 0, kvh * (p.block_size / 8) + tok_in_page / 8, (int)pid,
+                         policy);
       }
       __syncwarp();
-      if (!ok) break;
-      if (j == n_tiles - 1) {
-        // Slots past the request's length may hold anything (even NaN bits): zero those V rows so that a
-        // zero probability times V stays zero, then tell the MMA warp the stage is clean.
-        const bool landed = mbar_wait_bounded(&bars[kKvFull + s], (j / kKvStages) & 1u);
-        if (!__all_sync(0xffffffffu, landed)) {
-          if (lane == 0) raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
-          break;
-        }
+      return ok;
+    };
+    // Issue order K(0), K(1), V(0), K(2), V(1), ... follows the order in which the MMA warp consumes and
+    // frees the stages (S(j+1) is issued before P(j) V(j)).
+    bool ok = load_tile(&kmap, kOffK, kKFull, kKEmpty, 0);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      if (j + 1 < n_tiles) ok = load_tile(&kmap, kOffK, kKFull, kKEmpty, j + 1);
+      if (ok) ok = load_tile(&vmap, kOffV, kVFull, kVEmpty, j);
+    }
+    if (ok) {
+      // Slots past the request's length may hold anything (even NaN bits): zero those V rows of the last
+      // tile so that a zero probability times V stays zero, then tell the MMA warp the stage is clean.
+      const int j = n_tiles - 1, s = j % kKvStages;
+      const bool landed = mbar_wait_bounded(&bars[kVFull + s], (j / kKvStages) & 1u);
+      if (!__all_sync(0xffffffffu, landed)) {
+        if (lane == 0) raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+      } else {
         const long long first_bad = kv_len - (long long)j * kKv;  // rows >= first_bad are past the length
         uint8_t* vdst = smem + kOffV + s * kTile;
         for (int c = lane; c < kKv * 16; c += 32) {
           const int row = c >> 4, chunk = c & 15;
           if (row >= first_bad)
-            *reinterpret_cast<uint4*>(vdst + (chunk >> 3) * kHalfTile + row * 128 + (chunk & 7) * 16) =
-                make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(vdst + (row >> 3) * kGroupStride + (chunk >> 3) * kHalfStride + (row & 7) * 128 +
+                                      (chunk & 7) * 16) = make_uint4(0, 0, 0, 0);
         }
         fence_proxy_async_smem();
         __syncwarp();
@@ -184,32 +199,33 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr int kFmt = std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-      constexpr uint32_t idesc_s = instr_desc_f16(kKv, kFmt, 0);   // S = Q K^T : B = K, K-major
-      constexpr uint32_t idesc_o = instr_desc_f16(kDim, kFmt, 1);  // O += P V : B = V, MN-major
-      const uint32_t q_addr = smem_u32(smem + kOffQ), p_addr = smem_u32(smem + kOffP);
+      constexpr uint32_t idesc_s = instr_desc_f16(kKv, kFmt, 0);   // S = Q K^T : A = Q in TMEM, B = K, K-major
+      constexpr uint32_t idesc_o = instr_desc_f16(kDim, kFmt, 1);  // O += P V : A = P in TMEM, B = V, MN-major
       bool ok = mbar_wait_bounded(&bars[kQFull], 0);
+      // S(j) overwrites the TMEM buffer that held S(j-2) / P(j-2); P(j-2) V(j-2) was issued earlier by this
+      // thread and tcgen05.mma executes in issue order, so no barrier is needed for the reuse.
       auto issue_s = [&](int j) {
-        const int s = j % kKvStages;
-        if (!mbar_wait_bounded(&bars[kKvFull + s], (j / kKvStages) & 1u) ||
-            !mbar_wait_bounded(&bars[kSEmpty + s], ((j / kKvStages) & 1u) ^ 1u))
-          return false;
+        const int s = j % kKvStages, b = j & 1;
+        if (!mbar_wait_bounded(&bars[kKFull + s], (j / kKvStages) & 1u)) return false;
         tc_fence_after();
         const uint32_t k_addr = smem_u32(smem + kOffK + s * kTile);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {  // 8 x 16 dims
-          const uint32_t off = (ks >> 2) * kHalfTile + (ks & 3) * 32;
-          umma_f16(tmem_s + s * kKv, smem_desc_k128(q_addr + off), smem_desc_k128(k_addr + off), idesc_s,
-                   ks > 0 ? 1u : 0u);
+          const uint32_t off = (ks >> 2) * kHalfStride + (ks & 3) * 32;
+          umma_f16_ts(tmem_s + b * kKv, tmem_q + ks * 8, smem_desc_k128(k_addr + off, kGroupStride), idesc_s,
+                      ks > 0 ? 1u : 0u);
         }
-        umma_commit(&bars[kSFull + s]);
+        umma_commit(&bars[kKEmpty + s]);  // K stage free once these MMAs have read it
+        umma_commit(&bars[kSFull + b]);
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % kKvStages;
+        const int s = j % kKvStages, b = j & 1;
         if (j + 1 < n_tiles) ok = issue_s(j + 1);
         if (!ok) break;
-        if (!mbar_wait_bounded(&bars[kPFull], j & 1u) ||
+        if (!mbar_wait_bounded(&bars[kPFull + b], (j >> 1) & 1u) ||
+            !mbar_wait_bounded(&bars[kVFull + s], (j / kKvStages) & 1u) ||
             (j == n_tiles - 1 && !mbar_wait_bounded(&bars[kVClean], 0))) {
           ok = false;
           break;
@@ -217,13 +233,12 @@ __global__ void __launch_bounds__(kThreads, 1)
         tc_fence_after();
         const uint32_t v_addr = smem_u32(smem + kOffV + s * kTile);
 #pragma unroll
-        for (int kt = 0; kt < 8; ++kt) {  // 8 x 16 tokens
-          const uint64_t da = smem_desc_k128(p_addr + (kt >> 2) * kHalfTile + (kt & 3) * 32);
-          const uint64_t db = smem_desc_mn128(v_addr + kt * kSub * 128, kHalfTile, 1024);
-          umma_f16(tmem_o, da, db, idesc_o, (j > 0 || kt > 0) ? 1u : 0u);
+        for (int kt = 0; kt < 8; ++kt) {  // 8 x 16 tokens = 8 TMEM columns of packed P each
+          const uint64_t db = smem_desc_mn128(v_addr + kt * kBoxBytes, kHalfStride, kGroupStride);
+          umma_f16_ts(tmem_o, tmem_s + b * kKv + kt * 8, db, idesc_o, (j > 0 || kt > 0) ? 1u : 0u);
         }
-        umma_commit(&bars[kKvEmpty + s]);  // K/V stage free once these MMAs have read it
-        umma_commit(&bars[kPEmpty]);       // P tile free, O includes tile j
+        umma_commit(&bars[kVEmpty + s]);  // V stage free once these MMAs have read it
+        umma_commit(&bars[kPvDone + b]);  // O includes tile j
       }
       if (!ok) raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
     }
@@ -234,46 +249,75 @@ __global__ void __launch_bounds__(kThreads, 1)
     const bool row_live = tok_local < toks;
     const long long pos = row_live ? offset + i0 + tok_local : last_key;  // dead rows compute harmlessly
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    uint8_t* p_tile = smem + kOffP;
+    {
+      // Stage this thread's query row (128 16-bit values = 64 words) in TMEM, where it stays as the A
+      // operand of every S = Q K^T; rows past the chunk are zero.
+      const uint4* qrow = reinterpret_cast<const uint4*>(
+          reinterpret_cast<const T*>(p.query) + (q_begin + i0 + (row_live ? tok_local : 0)) * p.q_st +
+          (long long)(kvh * p.group + head_local) * p.q_sh);
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t w[32];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 v = row_live ? __ldg(qrow + h * 8 + i) : make_uint4(0, 0, 0, 0);
+          w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
+        }
+        tmem_st32(tmem_q + lane_addr + h * 32, w);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars[kQFull]);
+    }
+    // m_ref lives in the scaled log2 domain (score * scale * log2 e); scale > 0 is checked on the host, so
+    // the row maximum can be taken over the raw scores.
+    const float scale = p.scale_log2;
+    const long long first_pos = offset + i0;  // smallest query position of the tile
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const int s = j % kKvStages;
-      if (!mbar_wait_bounded(&bars[kSFull + s], (j / kKvStages) & 1u)) {
+      const int b = j & 1;
+      if (!mbar_wait_bounded(&bars[kSFull + b], (j >> 1) & 1u)) {
         ok = false;
         break;
       }
       tc_fence_after();
       float sv[kKv];
 #pragma unroll
-      for (int c = 0; c < kKv; c += 32) tmem_ld32(tmem_s + lane_addr + s * kKv + c, *reinterpret_cast<float(*)[32]>(&sv[c]));
+      for (int c = 0; c < kKv; c += 32) tmem_ld32(tmem_s + lane_addr + b * kKv + c, *reinterpret_cast<float(*)[32]>(&sv[c]));
       tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&bars[kSEmpty + s]);  // the S buffer may be overwritten by tile j + 2
       const long long key0 = (long long)j * kKv;
-      float mx = -INFINITY;
+      if (key0 + kKv - 1 > first_pos) {
+        // Only tiles that reach the causal diagonal (or the end of the request) carry masked keys.
+        const long long d = pos - key0;
+        const int lim = d < kKv - 1 ? (int)d : kKv - 1;  // keys [0, lim] of the tile are visible
 #pragma unroll
-      for (int c = 0; c < kKv; ++c) {
-        sv[c] = key0 + c <= pos ? sv[c] * p.scale_log2 : -INFINITY;
-        mx = fmaxf(mx, sv[c]);
+        for (int c = 0; c < kKv; ++c)
+          if (c > lim) sv[c] = -INFINITY;
       }
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+      for (int c = 0; c < kKv; c += 8) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) mx4[q] = fmaxf(mx4[q], fmaxf(sv[c + 2 * q], sv[c + 2 * q + 1]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;
       // Move the reference maximum only on the first tile or when this row outgrew it by 2^8.
       float alpha = 1.f;
       const bool grow = mx > m_ref + kRescaleThreshold || j == 0;
-      if (j > 0) {
-        if (!mbar_wait_bounded(&bars[kPEmpty], (j - 1) & 1u)) {  // P tile free and O holds tiles < j
+      if (grow) {
+        const float m_new = fmaxf(m_ref, mx);
+        alpha = ex2_approx(m_ref - m_new);  // 0 on the first tile
+        m_ref = m_new;
+      }
+      if (j > 0 && __any_sync(0xffffffffu, grow)) {
+        // Rescale this warp's 32 O rows in TMEM (rows that did not grow use alpha = 1); O must first hold
+        // every tile before this one.
+        if (!mbar_wait_bounded(&bars[kPvDone + ((j - 1) & 1)], ((j - 1) >> 1) & 1u)) {
           ok = false;
           break;
         }
         tc_fence_after();
-      }
-      if (grow) {
-        const float m_new = fmaxf(m_ref, mx);
-        alpha = exp2f(m_ref - m_new);  // 0 on the first tile
-        m_ref = m_new;
-      }
-      if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // Rescale this warp's 32 O rows in TMEM (rows that did not grow use alpha = 1).
 #pragma unroll
         for (int c = 0; c < kDim; c += 32) {
           float ov[32];
@@ -283,29 +327,29 @@ __global__ void __launch_bounds__(kThreads, 1)
           for (int i = 0; i < 32; ++i) ov[i] *= alpha;
           tmem_st32(tmem_o + lane_addr + c, ov);
         }
-        tmem_st_wait();
       }
       l *= alpha;
-      float sum = 0.f;
+      const float2 scale2 = make_float2(scale, scale), neg_m2 = make_float2(-m_ref, -m_ref);
+      float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-      for (int c = 0; c < kKv; c += 8) {
-        uint32_t w[4];
+      for (int h = 0; h < 2; ++h) {  // 64 keys = 32 packed columns per store
+        uint32_t w[32];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float p0 = exp2f(sv[c + 2 * q] - m_ref), p1 = exp2f(sv[c + 2 * q + 1] - m_ref);
-          sum += p0 + p1;
-          w[q] = Mma16816<T>::pack(p0, p1);
+        for (int q = 0; q < 32; ++q) {
+          float2 e = __ffma2_rn(make_float2(sv[h * 64 + 2 * q], sv[h * 64 + 2 * q + 1]), scale2, neg_m2);
+          e.x = ex2_approx(e.x);
+          e.y = ex2_approx(e.y);
+          sum2[q & 1] = __fadd2_rn(sum2[q & 1], e);
+          w[q] = Mma16816<T>::pack(e.x, e.y);
         }
-        const int chunk = c >> 3;  // 16-byte chunk = 8 tokens; 8 chunks per 64-token half
-        *reinterpret_cast<uint4*>(p_tile + (chunk >> 3) * kHalfTile + row * 128 + (((chunk & 7) ^ (row & 7)) << 4)) =
-            make_uint4(w[0], w[1], w[2], w[3]);
+        tmem_st32(tmem_s + lane_addr + b * kKv + h * 32, w);
       }
-      l += sum;
-      fence_proxy_async_smem();
+      l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars[kPFull]);
+      mbar_arrive(&bars[kPFull + b]);
     }
-    if (ok && !mbar_wait_bounded(&bars[kPEmpty], (n_tiles - 1) & 1u)) ok = false;
+    if (ok && !mbar_wait_bounded(&bars[kPvDone + ((n_tiles - 1) & 1)], ((n_tiles - 1) >> 1) & 1u)) ok = false;
     if (!ok) {
       raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
     } else {
@@ -339,33 +383,33 @@ __global__ void __launch_bounds__(kThreads, 1)
   }
 }
 
-struct QMapKey {
-  const void* ptr;
-  long long tokens, heads, st, sh;
-  int group, dtype;
-  bool operator==(const QMapKey& o) const {
-    return ptr == o.ptr && tokens == o.tokens && heads == o.heads && st == o.st && sh == o.sh && group == o.group &&
-           dtype == o.dtype;
+struct TileMapKey {
+  void* ptr;
+  long long s0, s2;
+  int num_blocks, kv_heads, block_size, dtype;
+  bool operator==(const TileMapKey& o) const {
+    return ptr == o.ptr && s0 == o.s0 && s2 == o.s2 && num_blocks == o.num_blocks && kv_heads == o.kv_heads &&
+           block_size == o.block_size && dtype == o.dtype;
   }
 };
-struct QMapHash {
-  size_t operator()(const QMapKey& k) const {
+struct TileMapKeyHash {
+  size_t operator()(const TileMapKey& k) const {
     size_t h = reinterpret_cast<size_t>(k.ptr);
-    h = h * 1000003u ^ (size_t)k.tokens;
-    h = h * 1000003u ^ (size_t)k.st;
-    h = h * 1000003u ^ (size_t)k.sh;
-    h = h * 1000003u ^ (size_t)(k.heads * 64 + k.group * 4 + k.dtype);
+    h = h * 1000003u ^ (size_t)k.s0;
+    h = h * 1000003u ^ (size_t)k.s2;
+    h = h * 1000003u ^ (size_t)(k.num_blocks * 131 + k.kv_heads * 17 + k.block_size * 3 + k.dtype);
     return h;
   }
 };
 
-// 3-D map over query [tokens, heads, 128]: box = 64 dims x `group` heads x (128 / group) tokens, which lands
-// as 128 rows of 128 bytes ordered (token, head).
-int query_tensor_map(const void* q, long long tokens, int heads, long long st, long long sh, int group, int dtype,
-                     CUtensorMap* out) {
+// 5-D map over pages [page, head, token, 128] whose box is one whole 16-token x 128-dim slab (4 KiB):
+//   d0 = 64 dims, d1 = token % 8, d2 = 64-dim half, d3 = (head, token / 8) merged, d4 = page.
+// Merging head and token / 8 needs head stride == block_size * token stride; the caller checks that.
+int page_tile_map(const mie_view4_t& pages, int num_blocks, int kv_heads, int block_size, int dtype,
+                  CUtensorMap* out) {
   static std::mutex mu;
-  static std::unordered_map<QMapKey, CUtensorMap, QMapHash> cache;
-  QMapKey key{q, tokens, heads, st, sh, group, dtype};
+  static std::unordered_map<TileMapKey, CUtensorMap, TileMapKeyHash> cache;
+  TileMapKey key{pages.ptr, pages.stride[0], pages.stride[2], num_blocks, kv_heads, block_size, dtype};
   {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
@@ -374,21 +418,29 @@ int query_tensor_map(const void* q, long long tokens, int heads, long long st, l
       return MIE_OK;
     }
   }
-  const uint64_t dims[3] = {(uint64_t)kDim, (uint64_t)heads, (uint64_t)tokens};
-  const uint64_t strides[2] = {(uint64_t)sh * 2, (uint64_t)st * 2};
-  const uint32_t box[3] = {64, (uint32_t)group, (uint32_t)(kRows / group)};
+  const uint64_t tok = (uint64_t)pages.stride[2] * 2;  // bytes between tokens
+  const uint64_t dims[5] = {64, 8, 2, (uint64_t)kv_heads * (block_size / 8), (uint64_t)num_blocks};
+  const uint64_t strides[4] = {tok, 128, 8 * tok, (uint64_t)pages.stride[0] * 2};
+  const uint32_t box[5] = {64, 8, 2, kSub / 8, 1};
   const int rc = make_tensor_map(out, dtype == MIE_DTYPE_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                               : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
-                                 3, const_cast<void*>(q), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+                                 5, pages.ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
   if (rc != MIE_OK) return rc;
   std::lock_guard<std::mutex> lock(mu);
-  if (cache.size() > 4096) cache.clear();
+  if (cache.size() > 8192) cache.clear();
   cache.emplace(key, *out);
   return MIE_OK;
 }
 
+bool pages_fit_tile_map(const mie_view4_t& v, int block_size) {
+  if (block_size % kSub != 0 || v.stride[3] != 1 || v.stride[2] != kDim) return false;
+  if (v.stride[1] != (long long)block_size * v.stride[2]) return false;
+  if (v.stride[0] <= 0 || (v.stride[0] * 2) % 16 != 0) return false;
+  return (reinterpret_cast<uintptr_t>(v.ptr) & 15) == 0;
+}
+
 template <typename T>
-int launch_umma(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensorMap& vmap,
+int launch_umma(const CUtensorMap& kmap, const CUtensorMap& vmap,
                 const UmmaPrefillParams& p, int q_tiles, cudaStream_t stream) {
   static bool configured[64] = {false};
   int dev = 0;
@@ -398,7 +450,7 @@ int launch_umma(const CUtensorMap& qmap, const CUtensorMap& kmap, const CUtensor
     configured[dev] = true;
   }
   dim3 grid((unsigned)q_tiles, (unsigned)p.requests, (unsigned)p.kv_heads);
-  prefill_umma_kernel<T><<<grid, kThreads, kSmemBytes, stream>>>(qmap, kmap, vmap, p, q_tiles);
+  prefill_umma_kernel<T><<<grid, kThreads, kSmemBytes, stream>>>(kmap, vmap, p, q_tiles);
   MIE_LAUNCH_CHECK("prefill_umma_kernel");
   return MIE_OK;
 }
@@ -417,18 +469,19 @@ int prefill_attention_umma(const void* query, long long q_st, long long q_sh, lo
   if (!(group == 1 || group == 2 || group == 4 || group == 8)) return MIE_ERR_UNSUPPORTED;
   if ((q_st * 2) % 16 || (q_sh * 2) % 16 || (reinterpret_cast<uintptr_t>(query) & 15)) return MIE_ERR_UNSUPPORTED;
   if ((o_st * 2) % 16 || (o_sh * 2) % 16 || (reinterpret_cast<uintptr_t>(out) & 15)) return MIE_ERR_UNSUPPORTED;
-  if (total_tokens <= 0) return MIE_ERR_UNSUPPORTED;
-  CUtensorMap qmap, kmap, vmap;
-  if (int rc = query_tensor_map(query, total_tokens, q_heads, q_st, q_sh, group, dtype, &qmap)) return rc;
-  if (int rc = page_tensor_map(key_blocks, num_blocks, kv_heads, block_size, dtype, &kmap)) return rc;
-  if (int rc = page_tensor_map(value_blocks, num_blocks, kv_heads, block_size, dtype, &vmap)) return rc;
-  UmmaPrefillParams p{(char*)out, o_st, o_sh, IndexView(block_tables), IndexView(cu_seqlens), IndexView(kv_lens),
+  if (total_tokens <= 0 || !(scale > 0.f)) return MIE_ERR_UNSUPPORTED;
+  if (!pages_fit_tile_map(key_blocks, block_size) || !pages_fit_tile_map(value_blocks, block_size))
+    return MIE_ERR_UNSUPPORTED;
+  CUtensorMap kmap, vmap;
+  if (int rc = page_tile_map(key_blocks, num_blocks, kv_heads, block_size, dtype, &kmap)) return rc;
+  if (int rc = page_tile_map(value_blocks, num_blocks, kv_heads, block_size, dtype, &vmap)) return rc;
+  UmmaPrefillParams p{(const char*)query, q_st, q_sh, (char*)out, o_st, o_sh, IndexView(block_tables), IndexView(cu_seqlens), IndexView(kv_lens),
                       requests, q_heads, kv_heads, group, block_size, num_blocks, table_width,
                       scale * 1.4426950408889634f, status};
   const int tok_per_tile = kRows / group;
   const int q_tiles = (max_query_len + tok_per_tile - 1) / tok_per_tile;
-  if (dtype == MIE_DTYPE_BF16) return launch_umma<__nv_bfloat16>(qmap, kmap, vmap, p, q_tiles, stream);
-  return launch_umma<__half>(qmap, kmap, vmap, p, q_tiles, stream);
+  if (dtype == MIE_DTYPE_BF16) return launch_umma<__nv_bfloat16>(kmap, vmap, p, q_tiles, stream);
+  return launch_umma<__half>(kmap, vmap, p, q_tiles, stream);
 }
 
 }  // namespace mie

@@ -66,11 +66,11 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 // K-major, 128-byte-swizzled shared-memory operand descriptor: rows are 128
 // bytes apart, 8-row groups 1024 bytes apart (the layout a 128-byte-wide TMA
 // box with SWIZZLE_128B writes).
-__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr) {
+__device__ __forceinline__ uint64_t smem_desc_k128(uint32_t smem_addr, uint32_t sbo_bytes = 1024) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3ffff) >> 4);  // start address
   d |= (uint64_t)1 << 16;                       // leading byte offset (unused with swizzle)
-  d |= (uint64_t)(1024 >> 4) << 32;             // stride byte offset
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fff) << 32;  // stride byte offset: distance between 8-row groups
   d |= (uint64_t)1 << 46;                       // descriptor version (Blackwell)
   d |= (uint64_t)2 << 61;                       // SWIZZLE_128B
   return d;
@@ -94,8 +94,19 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
       : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
-  const uint32_t* r = reinterpret_cast<const uint32_t*>(v);
+// Same MMA with the A operand read from tensor memory (row = lane, two 16-bit elements per 32-bit column,
+// K = 16 elements = 8 columns per instruction).
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
@@ -106,6 +117,9 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
         "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
         "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
       : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  tmem_st32(taddr, *reinterpret_cast<const uint32_t(*)[32]>(&v));
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
