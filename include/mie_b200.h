@@ -328,6 +328,59 @@ int mie_qkv_norm_rope_write(const void* qkv, int64_t ld, const void* q_weight, c
                             int32_t kv_heads, int32_t block_size, int32_t num_blocks, int32_t table_rows,
                             int32_t table_width, float eps, int32_t* status, void* stream);
 
+/* ---------------------------------------------------------------------------
+ * Tensor-parallel exchange (no counterpart in the reference, which runs on one
+ * GPU; these serve the head-sharded TP = 2/4/8 decode step).
+ * ------------------------------------------------------------------------- */
+
+#define MIE_TP_MAX_RANKS 8
+#define MIE_IPC_HANDLE_BYTES 64
+
+/*
+ * Sharing one device buffer between the ranks of a node.  mie_ipc_export fills
+ * `handle` (MIE_IPC_HANDLE_BYTES, cudaIpcGetMemHandle of the allocation that
+ * contains ptr) and the byte offset of ptr inside that allocation; the bytes
+ * travel to the other processes by any host channel.  mie_ipc_open maps a
+ * peer's buffer into this process with peer access enabled and returns the
+ * address that corresponds to the exported ptr; mie_ipc_close unmaps it.  The
+ * exporter must keep the allocation alive while it is mapped elsewhere.
+ */
+int mie_ipc_export(const void* ptr, uint8_t* handle, int64_t* offset);
+int mie_ipc_open(const uint8_t* handle, int64_t offset, void** mapped);
+int mie_ipc_close(void* mapped, int64_t offset);
+
+/* Per-rank addresses (entry r = rank r's buffer as mapped in THIS process;
+ * entry `rank` is the local buffer). */
+typedef struct {
+  const void* partial[MIE_TP_MAX_RANKS]; /* row-parallel GEMM output [rows, ld_partial] bf16 */
+  void* q[MIE_TP_MAX_RANKS];             /* e4m3 rows [rows, ldq] for the next GEMM, or all NULL */
+  float* scales[MIE_TP_MAX_RANKS];       /* their scales [cols / 128, scale_ld] */
+  void* normed[MIE_TP_MAX_RANKS];        /* bf16 rows [rows, cols], or all NULL */
+  uint32_t* flags[MIE_TP_MAX_RANKS];     /* 2 * MIE_TP_MAX_RANKS epoch words per rank, zeroed once */
+} mie_tp_peers_t;
+
+/*
+ * All-reduce fused into the residual add + RMSNorm (+ quantisation) that
+ * follows o_proj / down_proj under tensor parallelism; replaces
+ * all_reduce(partial) followed by mie_rms_norm(partial, residual, ...).
+ * Rank `rank` owns rows [rank * ceil(rows / tp), ...): for those rows it sums
+ * the partial rows of all ranks (fp32, rank order, rounded once to bf16),
+ * adds residual (local, [rows, cols], only the owned rows are read), writes
+ * the sum to summed (local, owned rows only), normalises with weight / eps
+ * and stores the result into EVERY rank's q + scales and/or normed buffers.
+ * The kernel first waits until every peer's partial buffer is complete and
+ * returns only after every peer's rows have landed locally, so the next launch
+ * on the stream may read the whole [rows, cols] result.  state: two zeroed
+ * uint32 words of local device memory owned by this call site (epoch, arrival
+ * counter); all ranks must make the same sequence of calls.  Waits give up
+ * after max_polls polls (0 = default, about two seconds) and set
+ * MIE_STATUS_WAIT_TIMEOUT; no multimem / NVLS, plain peer loads and stores.
+ */
+int mie_tp_reduce_rms_norm(const mie_tp_peers_t* peers, int32_t tp, int32_t rank, int64_t ld_partial,
+                           const void* residual, void* summed, const void* weight, int64_t ldq, int32_t scale_ld,
+                           int32_t rows, int32_t cols, float eps, uint32_t* state, uint32_t max_polls,
+                           int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

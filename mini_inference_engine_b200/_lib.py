@@ -47,6 +47,18 @@ class View4T(Structure):
     _fields_ = [("ptr", c_void_p), ("stride", c_int64 * 4)]
 
 
+TP_MAX_RANKS = 8
+IPC_HANDLE_BYTES = 64
+
+
+class TpPeersT(ctypes.Structure):
+    """``mie_tp_peers_t``: per-rank addresses of the buffers of the fused tensor-parallel exchange."""
+
+    _fields_ = [("partial", c_void_p * TP_MAX_RANKS), ("q", c_void_p * TP_MAX_RANKS),
+                ("scales", c_void_p * TP_MAX_RANKS), ("normed", c_void_p * TP_MAX_RANKS),
+                ("flags", c_void_p * TP_MAX_RANKS)]
+
+
 _SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "mie_last_error": (c_char_p, []),
     "mie_version": (ctypes.c_int, []),
@@ -91,6 +103,12 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "mie_qkv_norm_rope_write": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, IndexT,
                                                IndexT, IndexT, c_void_p, View4T, View4T, c_int32, c_int32, c_int32,
                                                c_int32, c_int32, c_int32, c_int32, c_float, c_void_p, c_void_p]),
+    "mie_ipc_export": (ctypes.c_int, [c_void_p, c_void_p, ctypes.POINTER(c_int64)]),
+    "mie_ipc_open": (ctypes.c_int, [c_void_p, c_int64, ctypes.POINTER(c_void_p)]),
+    "mie_ipc_close": (ctypes.c_int, [c_void_p, c_int64]),
+    "mie_tp_reduce_rms_norm": (ctypes.c_int, [ctypes.POINTER(TpPeersT), c_int32, c_int32, c_int64, c_void_p, c_void_p,
+                                              c_void_p, c_int64, c_int32, c_int32, c_int32, c_float, c_void_p,
+                                              ctypes.c_uint32, c_void_p, c_void_p]),
 }
 
 _lib: ctypes.CDLL | None = None

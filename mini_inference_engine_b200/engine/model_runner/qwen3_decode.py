@@ -23,12 +23,14 @@ and greedy sampling exchanges one (value, index) pair per row.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import torch
 
 from ... import _lib
 from ..kernels import sm89_fp8
+from .peer_exchange import PeerExchange
 from ..kv_cache.triton_paged_attention import decode_scratch, launch_decode_attention
 
 
@@ -207,7 +209,7 @@ class Qwen3DecodeRunner:
     """Decode steps of a Qwen3-shaped FP8 model over paged KV, eager or as a CUDA graph."""
 
     def __init__(self, weights: Qwen3Weights, *, num_pages: int, max_batch: int, max_context: int,
-                 process_group=None, kv_init: str = "zeros") -> None:
+                 process_group=None, kv_init: str = "zeros", fused_exchange: bool | None = None) -> None:
         self.weights, self.shape = weights, weights.shape
         self.device, self.group = weights.device, process_group
         self.tp = weights.tp_size
@@ -233,6 +235,13 @@ class Qwen3DecodeRunner:
                                       max_batch * max_context, self.device)
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, DecodeBuffers]] = {}
         self.launches_per_step = 0
+        # Tensor parallel decode: the all-reduce after o_proj / down_proj is fused into the residual add +
+        # RMSNorm + quantisation kernel over peer memory unless MIE_TP_EXCHANGE=nccl (or fused_exchange=False).
+        if fused_exchange is None:
+            fused_exchange = os.environ.get("MIE_TP_EXCHANGE", "fused") != "nccl"
+        self.exchange = None
+        if self.tp > 1 and fused_exchange:
+            self.exchange = PeerExchange(self.tp, weights.tp_rank, max_batch, shape.hidden, self.device, process_group)
 
     # -- small helpers ------------------------------------------------------------------------
 
@@ -261,8 +270,9 @@ class Qwen3DecodeRunner:
                                     self.shape.rms_eps, stream))
         return out, summed, None
 
-    def _gemm(self, quantized, weight, weight_scale, rows: int, k: int) -> torch.Tensor:
-        out = torch.empty(rows, weight.shape[0], dtype=torch.bfloat16, device=self.device)
+    def _gemm(self, quantized, weight, weight_scale, rows: int, k: int, out: torch.Tensor | None = None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty(rows, weight.shape[0], dtype=torch.bfloat16, device=self.device)
         sm89_fp8.launch_fp8_gemm(quantized[0], quantized[1], weight, weight_scale, out, rows, k, status=self.status)
         return out
 
@@ -273,6 +283,23 @@ class Qwen3DecodeRunner:
         if self.tp > 1:
             torch.distributed.all_reduce(x, group=self.group)
         return x
+
+    def _row_parallel_then_norm(self, quantized, weight, weight_scale, rows: int, k: int, residual, norm_weight,
+                                *, quantize: bool):
+        """Row-parallel projection, sum over the ranks, residual add and RMSNorm of the sum.  Returns
+        ``(normed bf16 or None, new residual, quantised pair or None)`` like ``_norm``.  With the fused exchange
+        the new residual is only valid in the rows this rank owns (the only rows it reads again)."""
+
+        ex = self.exchange
+        if ex is None:
+            out = self._all_reduce(self._gemm(quantized, weight, weight_scale, rows, k))
+            return self._norm(out, norm_weight, residual, quantize=quantize)
+        self._gemm(quantized, weight, weight_scale, rows, k, out=ex.partial[:rows])
+        summed = torch.empty_like(residual)
+        ex.reduce_norm(rows, residual, summed, norm_weight, self.shape.rms_eps, quantized=quantize, status=self.status)
+        if quantize:
+            return None, summed, (ex.q[:rows], ex.scales[:, :rows])
+        return ex.normed[:rows], summed, None
 
     # -- the decode forward -------------------------------------------------------------------
 
@@ -288,14 +315,11 @@ class Qwen3DecodeRunner:
         hd, lq, lkv = shape.head_dim, self.local_q_heads, self.local_kv_heads
         hidden = self.weights.embedding.index_select(0, input_ids)
         positions = sequence_lengths - 1
-        residual, mlp_out = None, None
         scale = 1.0 / math.sqrt(hd)
-        for index, layer in enumerate(self.weights.layers):
-            if index == 0:
-                _, _, quantized = self._norm(hidden, layer.input_norm, quantize=True)
-                residual = hidden
-            else:
-                _, residual, quantized = self._norm(mlp_out, layer.input_norm, residual, quantize=True)
+        layers = self.weights.layers
+        _, _, quantized = self._norm(hidden, layers[0].input_norm, quantize=True)
+        residual, final = hidden, None
+        for index, layer in enumerate(layers):
             qkv = self._gemm(quantized, layer.qkv, layer.qkv_scale, batch, shape.hidden)
             queries = torch.empty(batch, lq, 1, hd, dtype=torch.bfloat16, device=self.device)
             _lib.check(lib.mie_qkv_norm_rope_write(
@@ -311,8 +335,8 @@ class Qwen3DecodeRunner:
                                     max_total_tokens=batch * self.max_context, scratch=self.scratch,
                                     split_policy=1, use_plan=index > 0, plan_slot=index, status=self.status,
                                     quantized_out=attn_q)
-            attn_out = self._all_reduce(self._gemm(attn_q, layer.o, layer.o_scale, batch, lq * hd))
-            _, residual, quantized = self._norm(attn_out, layer.post_norm, residual, quantize=True)
+            _, residual, quantized = self._row_parallel_then_norm(attn_q, layer.o, layer.o_scale, batch, lq * hd,
+                                                                  residual, layer.post_norm, quantize=True)
             gate_up = self._gemm(quantized, layer.gate_up, layer.gate_up_scale, batch, shape.hidden)
             inter = self.local_inter
             if inter % 128 == 0:
@@ -326,8 +350,10 @@ class Qwen3DecodeRunner:
                 _lib.check(lib.mie_silu_mul(_lib.ptr(gate_up), _lib.ptr(gate_up[:, inter:]), gate_up.stride(0),
                                             _lib.ptr(act), None, 0, None, 0, batch, inter, stream))
                 act_q = self._quantize(act)
-            mlp_out = self._all_reduce(self._gemm(act_q, layer.down, layer.down_scale, batch, inter))
-        final, _, _ = self._norm(mlp_out, self.weights.final_norm, residual, quantize=False)
+            last = index + 1 == len(layers)
+            next_norm = self.weights.final_norm if last else layers[index + 1].input_norm
+            final, residual, quantized = self._row_parallel_then_norm(act_q, layer.down, layer.down_scale, batch, inter,
+                                                                      residual, next_norm, quantize=not last)
         logits = torch.matmul(final, self.weights.lm_head.t())
         self.launches_per_step = int(lib.mie_launch_count() - launches_before)
         if self.tp == 1:
