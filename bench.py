@@ -435,6 +435,8 @@ def main() -> None:
                 "split_kv": "length-proportional chunks chosen on the device",
                 "l2": "inputs larger than L2 (KV pool and weights are re-read from HBM every step)",
                 "graph": "one CUDA graph per decode step",
+                "tp_exchange": ("none" if tp == 1 else "fused reduce+norm over peer memory"
+                                if runner.exchange is not None else "nccl all-reduce"),
             },
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
             "gpu_launches": launches_per_step * steps, "clocks": clocks,
