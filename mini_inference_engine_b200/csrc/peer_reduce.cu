@@ -92,12 +92,20 @@ __global__ void __launch_bounds__(1024) peer_reduce_norm_kernel(PeerReduceParams
     float v[8];
     float ss = 0.f;
     if (active) {
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int r = 0; r < p.tp; ++r) {
-        float part[8];
-        unpack8(ld_volatile_v4(p.partial[r] + row * p.ld_partial + c0), part);
+      // All ranks' loads are issued before the first one is used: one NVLink round trip, not tp of them.
+      uint4 raw[kMaxRanks];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += part[j];
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < p.tp) raw[r] = ld_volatile_v4(p.partial[r] + row * p.ld_partial + c0);
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r) {
+        if (r < p.tp) {
+          float part[8];
+          unpack8(raw[r], part);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += part[j];
+        }
       }
       float res[8];
       unpack8(*reinterpret_cast<const uint4*>(p.residual + row * p.cols + c0), res);

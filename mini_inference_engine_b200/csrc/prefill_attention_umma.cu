@@ -4,14 +4,14 @@
 // heads that share one KV head, so a K/V tile staged once serves the whole GQA group.  Per 128-token K/V
 // tile:
 //   S = Q K^T      UMMA 128x128x16 (bf16/fp16, fp32 accumulate) into one of two TMEM buffers;
-//   softmax        128 threads, one query row each, read their S row from TMEM, apply the causal /
+//   softmax        256 threads, two per query row, read their half of the S row from TMEM, apply the causal /
 //                  length mask and an exp2 softmax against a running reference maximum, and write
 //                  P (16-bit, two per column) back into TMEM over the S buffer they just read;
 //   O += P V       UMMA 128x128x16 with P as the TMEM A operand and V as the MN-major shared-memory B
 //                  operand, accumulated in TMEM over all tiles.
 // The reference maximum is only moved when a row's maximum grows by more than 2^8 (then that warp
 // rescales its O rows in TMEM), so O is read from TMEM once, at the end.
-// Warp roles: 4 softmax warps, 1 TMA producer (K/V pages gathered through the block table, one 4 KiB
+// Warp roles: 8 softmax warps (two threads per query row), 1 TMA producer (K/V pages gathered through the block table, one 4 KiB
 // box per 16-token page slab, 128-byte swizzle, no multicast), 1 MMA issuer that also owns
 // the TMEM allocation.  Every wait is bounded and reports MIE_STATUS_WAIT_TIMEOUT.
 #include <mutex>
@@ -39,7 +39,8 @@ constexpr int kTile = kKv * kDim * 2;            // 32 KiB: one K or V tile
 constexpr int kGroupStride = 2048;
 constexpr int kHalfStride = 1024;
 constexpr int kKvStages = 3;                     // K and V each have their own ring of this depth
-constexpr int kSoftmaxWarps = 4;
+constexpr int kSoftmaxWarps = 8;                 // two threads per query row: each owns 64 of the 128 keys / dims
+constexpr int kHalf = 64;
 constexpr int kThreads = (kSoftmaxWarps + 2) * 32;
 constexpr float kRescaleThreshold = 8.0f;        // log2 units
 
@@ -47,7 +48,10 @@ constexpr float kRescaleThreshold = 8.0f;        // log2 units
 constexpr int kOffK = 0;
 constexpr int kOffV = kOffK + kKvStages * kTile;
 constexpr int kOffBar = kOffV + kKvStages * kTile;
-constexpr int kSmemBytes = kOffBar + 256 + 1024;
+constexpr int kOffXchg = kOffBar + 256;          // [tile parity][key half][row] floats: the row pairs' exchange
+constexpr int kOffIds = kOffXchg + 2 * 2 * kRows * 4;  // page id of every 16-token box of the request
+constexpr int kMaxIds = 4096;                          // 64k tokens of context
+constexpr int kSmemBytes = kOffIds + kMaxIds * 4 + 1024;
 
 struct UmmaPrefillParams {
   const char* query;
@@ -119,6 +123,24 @@ __global__ void __launch_bounds__(kThreads, 1)
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
+  {
+    // All threads fetch the block-table entries of the boxes this CTA will read (independent loads, all
+    // in flight together), so the producer never waits on a dependent global load between TMA issues.
+    int* ids = reinterpret_cast<int*>(smem + kOffIds);
+    const int n_ids = n_tiles * (kKv / kSub) < kMaxIds ? n_tiles * (kKv / kSub) : kMaxIds;
+    for (int i = threadIdx.x; i < n_ids; i += kThreads) {
+      const long long tok = (long long)i * kSub;
+      long long pid = 0;
+      if (tok <= last_key) {
+        pid = p.tables.at(r, tok / p.block_size);
+        if (pid < 0 || pid >= p.num_blocks) {
+          raise_status(p.status, MIE_STATUS_BAD_PAGE);
+          pid = 0;
+        }
+      }
+      ids[i] = (int)pid;
+    }
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -133,20 +155,14 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint64_t policy = l2_evict_first_policy();
     // One 128-token K or V tile = eight 16-token boxes per 64-dim half.  Lanes 0..7 each own one box row,
     // so the eight block-table lookups (dependent global loads) run in parallel.
+    const int* page_ids = reinterpret_cast<const int*>(smem + kOffIds);
     auto load_tile = [&](const CUtensorMap* map, int off_base, int full0, int empty0, int j) -> bool {
       const int s = j % kKvStages;
-      long long pid = 0;
-      int tok_in_page = 0;
+      int pid = 0, tok_in_page = 0;
       if (lane < kKv / kSub) {
         const long long tok = (long long)j * kKv + lane * kSub;
-        if (tok <= last_key) {
-          pid = p.tables.at(r, tok / p.block_size);
-          tok_in_page = (int)(tok % p.block_size);
-          if (pid < 0 || pid >= p.num_blocks) {
-            raise_status(p.status, MIE_STATUS_BAD_PAGE);
-            pid = 0;
-          }
-        }
+        pid = page_ids[j * (kKv / kSub) + lane];
+        if (tok <= last_key) tok_in_page = (int)(tok % p.block_size);
       }
       bool ok = true;
       if (lane == 0) {
@@ -243,28 +259,33 @@ __global__ void __launch_bounds__(kThreads, 1)
       if (!ok) raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
     }
   } else {
-    // ---------------- Softmax warps: one query row per thread ----------------
-    const int row = warp * 32 + lane;                       // TMEM lane = row of the tile
+    // ---------------- Softmax warps: two threads per query row ----------------
+    // Warps w and w + 4 share TMEM lane quadrant w % 4 (the same 32 rows); the first takes keys / output
+    // dims [0, 64), the second [64, 128).  The pair meets on a named barrier once per tile to combine the
+    // row maximum.  A failed wait only clears `ok` (later waits are skipped) so that both threads of a pair
+    // always pass the same number of pair barriers.
+    const int quad = warp & 3, half = warp >> 2;
+    const int row = quad * 32 + lane;                       // TMEM lane = row of the tile
+    const int cbase = half * kHalf;
     const int tok_local = row / p.group, head_local = row % p.group;
     const bool row_live = tok_local < toks;
     const long long pos = row_live ? offset + i0 + tok_local : last_key;  // dead rows compute harmlessly
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    const uint32_t lane_addr = (uint32_t)(quad * 32) << 16;
+    float* xchg = reinterpret_cast<float*>(smem + kOffXchg);
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory"); };
     {
-      // Stage this thread's query row (128 16-bit values = 64 words) in TMEM, where it stays as the A
-      // operand of every S = Q K^T; rows past the chunk are zero.
+      // Stage this thread's half of the query row (64 16-bit values = 32 words) in TMEM, where it stays as
+      // the A operand of every S = Q K^T; rows past the chunk are zero.
       const uint4* qrow = reinterpret_cast<const uint4*>(
           reinterpret_cast<const T*>(p.query) + (q_begin + i0 + (row_live ? tok_local : 0)) * p.q_st +
-          (long long)(kvh * p.group + head_local) * p.q_sh);
+          (long long)(kvh * p.group + head_local) * p.q_sh + cbase);
+      uint32_t w[32];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t w[32];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const uint4 v = row_live ? __ldg(qrow + h * 8 + i) : make_uint4(0, 0, 0, 0);
-          w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
-        }
-        tmem_st32(tmem_q + lane_addr + h * 32, w);
+      for (int i = 0; i < 8; ++i) {
+        const uint4 v = row_live ? __ldg(qrow + i) : make_uint4(0, 0, 0, 0);
+        w[4 * i] = v.x, w[4 * i + 1] = v.y, w[4 * i + 2] = v.z, w[4 * i + 3] = v.w;
       }
+      tmem_st32(tmem_q + lane_addr + half * 32, w);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[kQFull]);
@@ -273,36 +294,39 @@ __global__ void __launch_bounds__(kThreads, 1)
     // the row maximum can be taken over the raw scores.
     const float scale = p.scale_log2;
     const long long first_pos = offset + i0;  // smallest query position of the tile
-    float m_ref = -INFINITY, l = 0.f;
+    float m_ref = -INFINITY, l = 0.f;         // l: this thread's half of the row sum
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
+    for (int j = 0; j < n_tiles; ++j) {
       const int b = j & 1;
-      if (!mbar_wait_bounded(&bars[kSFull + b], (j >> 1) & 1u)) {
-        ok = false;
-        break;
-      }
+      if (ok && !mbar_wait_bounded(&bars[kSFull + b], (j >> 1) & 1u)) ok = false;
       tc_fence_after();
-      float sv[kKv];
+      float sv[kHalf];
 #pragma unroll
-      for (int c = 0; c < kKv; c += 32) tmem_ld32(tmem_s + lane_addr + b * kKv + c, *reinterpret_cast<float(*)[32]>(&sv[c]));
+      for (int c = 0; c < kHalf; c += 32)
+        tmem_ld32(tmem_s + lane_addr + b * kKv + cbase + c, *reinterpret_cast<float(*)[32]>(&sv[c]));
       tmem_ld_wait();
       const long long key0 = (long long)j * kKv;
       if (key0 + kKv - 1 > first_pos) {
         // Only tiles that reach the causal diagonal (or the end of the request) carry masked keys.
-        const long long d = pos - key0;
-        const int lim = d < kKv - 1 ? (int)d : kKv - 1;  // keys [0, lim] of the tile are visible
+        const long long d = pos - key0 - cbase;
+        const int lim = d < kHalf - 1 ? (int)(d < -1 ? -1 : d) : kHalf - 1;  // keys [0, lim] of this half are visible
 #pragma unroll
-        for (int c = 0; c < kKv; ++c)
+        for (int c = 0; c < kHalf; ++c)
           if (c > lim) sv[c] = -INFINITY;
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < kKv; c += 8) {
+      for (int c = 0; c < kHalf; c += 8) {
 #pragma unroll
         for (int q = 0; q < 4; ++q) mx4[q] = fmaxf(mx4[q], fmaxf(sv[c + 2 * q], sv[c + 2 * q + 1]));
       }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale;
-      // Move the reference maximum only on the first tile or when this row outgrew it by 2^8.
+      const float mx_half = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // Both halves have read their S columns before either writes P over them (the barrier below).
+      xchg[(b * 2 + half) * kRows + row] = mx_half;
+      pair_sync();
+      const float mx = fmaxf(mx_half, xchg[(b * 2 + (half ^ 1)) * kRows + row]) * scale;
+      // Move the reference maximum only on the first tile or when this row outgrew it by 2^8 (both threads
+      // of the row see the same mx and decide alike).
       float alpha = 1.f;
       const bool grow = mx > m_ref + kRescaleThreshold || j == 0;
       if (grow) {
@@ -311,44 +335,42 @@ __global__ void __launch_bounds__(kThreads, 1)
         m_ref = m_new;
       }
       if (j > 0 && __any_sync(0xffffffffu, grow)) {
-        // Rescale this warp's 32 O rows in TMEM (rows that did not grow use alpha = 1); O must first hold
-        // every tile before this one.
-        if (!mbar_wait_bounded(&bars[kPvDone + ((j - 1) & 1)], ((j - 1) >> 1) & 1u)) {
-          ok = false;
-          break;
-        }
+        // Rescale this warp's 32 rows x 64 dims of O in TMEM (rows that did not grow use alpha = 1); O must
+        // first hold every tile before this one.
+        if (ok && !mbar_wait_bounded(&bars[kPvDone + ((j - 1) & 1)], ((j - 1) >> 1) & 1u)) ok = false;
         tc_fence_after();
 #pragma unroll
-        for (int c = 0; c < kDim; c += 32) {
+        for (int c = 0; c < kHalf; c += 32) {
           float ov[32];
-          tmem_ld32(tmem_o + lane_addr + c, ov);
+          tmem_ld32(tmem_o + lane_addr + cbase + c, ov);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) ov[i] *= alpha;
-          tmem_st32(tmem_o + lane_addr + c, ov);
+          tmem_st32(tmem_o + lane_addr + cbase + c, ov);
         }
       }
       l *= alpha;
       const float2 scale2 = make_float2(scale, scale), neg_m2 = make_float2(-m_ref, -m_ref);
       float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+      uint32_t w[32];  // 64 keys = 32 packed columns
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {  // 64 keys = 32 packed columns per store
-        uint32_t w[32];
-#pragma unroll
-        for (int q = 0; q < 32; ++q) {
-          float2 e = __ffma2_rn(make_float2(sv[h * 64 + 2 * q], sv[h * 64 + 2 * q + 1]), scale2, neg_m2);
-          e.x = ex2_approx(e.x);
-          e.y = ex2_approx(e.y);
-          sum2[q & 1] = __fadd2_rn(sum2[q & 1], e);
-          w[q] = Mma16816<T>::pack(e.x, e.y);
-        }
-        tmem_st32(tmem_s + lane_addr + b * kKv + h * 32, w);
+      for (int q = 0; q < 32; ++q) {
+        float2 e = __ffma2_rn(make_float2(sv[2 * q], sv[2 * q + 1]), scale2, neg_m2);
+        e.x = ex2_approx(e.x);
+        e.y = ex2_approx(e.y);
+        sum2[q & 1] = __fadd2_rn(sum2[q & 1], e);
+        w[q] = Mma16816<T>::pack(e.x, e.y);
       }
+      tmem_st32(tmem_s + lane_addr + b * kKv + half * 32, w);
       l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bars[kPFull + b]);
     }
+    // Row sum = this half + the partner's.
+    xchg[((n_tiles & 1) * 2 + half) * kRows + row] = l;
+    pair_sync();
+    l += xchg[((n_tiles & 1) * 2 + (half ^ 1)) * kRows + row];
     if (ok && !mbar_wait_bounded(&bars[kPvDone + ((n_tiles - 1) & 1)], ((n_tiles - 1) >> 1) & 1u)) ok = false;
     if (!ok) {
       raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
@@ -356,11 +378,11 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const float inv = 1.f / fmaxf(l, 1.17549435e-38f);
       T* orow = reinterpret_cast<T*>(p.out) + (q_begin + i0 + tok_local) * p.o_st +
-                (long long)(kvh * p.group + head_local) * p.o_sh;
+                (long long)(kvh * p.group + head_local) * p.o_sh + cbase;
 #pragma unroll
-      for (int c = 0; c < kDim; c += 32) {
+      for (int c = 0; c < kHalf; c += 32) {
         float ov[32];
-        tmem_ld32(tmem_o + lane_addr + c, ov);
+        tmem_ld32(tmem_o + lane_addr + cbase + c, ov);
         tmem_ld_wait();
         if (row_live) {
 #pragma unroll
@@ -472,6 +494,7 @@ int prefill_attention_umma(const void* query, long long q_st, long long q_sh, lo
   if (total_tokens <= 0 || !(scale > 0.f)) return MIE_ERR_UNSUPPORTED;
   if (!pages_fit_tile_map(key_blocks, block_size) || !pages_fit_tile_map(value_blocks, block_size))
     return MIE_ERR_UNSUPPORTED;
+  if ((long long)table_width * block_size / kSub + kKv / kSub > kMaxIds) return MIE_ERR_UNSUPPORTED;
   CUtensorMap kmap, vmap;
   if (int rc = page_tile_map(key_blocks, num_blocks, kv_heads, block_size, dtype, &kmap)) return rc;
   if (int rc = page_tile_map(value_blocks, num_blocks, kv_heads, block_size, dtype, &vmap)) return rc;
