@@ -356,7 +356,7 @@ typedef struct {
   void* q[MIE_TP_MAX_RANKS];             /* e4m3 rows [rows, ldq] for the next GEMM, or all NULL */
   float* scales[MIE_TP_MAX_RANKS];       /* their scales [cols / 128, scale_ld] */
   void* normed[MIE_TP_MAX_RANKS];        /* bf16 rows [rows, cols], or all NULL */
-  uint32_t* flags[MIE_TP_MAX_RANKS];     /* 2 * MIE_TP_MAX_RANKS epoch words per rank, zeroed once */
+  uint32_t* flags[MIE_TP_MAX_RANKS];     /* 2 * MIE_TP_MAX_RANKS words per rank (epochs + a counter), zeroed once */
 } mie_tp_peers_t;
 
 /*
@@ -370,9 +370,10 @@ typedef struct {
  * and stores the result into EVERY rank's q + scales and/or normed buffers.
  * The kernel first waits until every peer's partial buffer is complete and
  * returns only after every peer's rows have landed locally, so the next launch
- * on the stream may read the whole [rows, cols] result.  state: two zeroed
- * uint32 words of local device memory owned by this call site (epoch, arrival
- * counter); all ranks must make the same sequence of calls.  Waits give up
+ * on the stream may read the whole [rows, cols] result.  state: four zeroed
+ * uint32 words of local device memory that belong to this set of flags
+ * (epoch, arrival counter, rows landed); all ranks must make the same
+ * sequence of calls with the same rows.  Waits give up
  * after max_polls polls (0 = default, about two seconds) and set
  * MIE_STATUS_WAIT_TIMEOUT; no multimem / NVLS, plain peer loads and stores.
  */

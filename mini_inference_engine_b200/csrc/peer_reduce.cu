@@ -10,7 +10,8 @@
 //      value), adds the residual, normalises, and
 //   3. stores the result the next column-parallel GEMM needs - e4m3 rows + per-128 scales, or bf16 rows -
 //      straight into every rank's input buffer (peer stores), then
-//   4. tells the peers "my rows have landed" and waits until all of theirs have.
+//   4. counts each finished row into the peers' "rows landed" counters (one remote atomic per CTA and peer,
+//      after a system-scope fence) and waits until its own counter shows every peer's rows.
 // The residual stream stays sharded by rows (a rank only ever updates the rows it owns), so the wire
 // carries (tp-1)/tp of the partial sums once plus the 1-byte activations, about half of what a bf16
 // all-reduce moves, and the separate norm/quantise launch disappears.
@@ -33,14 +34,14 @@ struct PeerReduceParams {
   uint8_t* q[kMaxRanks];
   float* scales[kMaxRanks];
   __nv_bfloat16* normed[kMaxRanks];
-  unsigned* flags[kMaxRanks];  // rank r's flag block: [0..8) "partial ready" epochs, [8..16) "rows landed" epochs
-  unsigned* state;             // local: [0] last finished epoch, [1] CTA arrival counter
+  unsigned* flags[kMaxRanks];  // rank r's flag block: [0..8) "partial ready" epochs, [8] count of rows landed
+  unsigned* state;             // local: [0] last finished epoch, [1] CTA arrival counter, [2] rows landed so far
   const __nv_bfloat16* residual;
   __nv_bfloat16* summed;
   const __nv_bfloat16* weight;
   long long ld_partial, ldq;
   int scale_ld;
-  int tp, rank, cols, row_begin, row_count;
+  int tp, rank, rows, cols, row_begin, row_count;
   float eps;
   int* status;
   unsigned max_polls;
@@ -67,14 +68,16 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
 __device__ __forceinline__ bool wait_epoch(const unsigned* flag, unsigned epoch, unsigned max_polls) {
   for (unsigned i = 0; i < max_polls; ++i) {
     if ((int)(ld_acquire_sys(flag) - epoch) >= 0) return true;
-    if (i > 16) __nanosleep(64);
+    if (i > 4096) __nanosleep(128);  // a late peer: stop hammering the memory system
   }
   return false;
+}
+__device__ __forceinline__ void red_add_sys(unsigned* p, unsigned v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __global__ void __launch_bounds__(1024) peer_reduce_norm_kernel(PeerReduceParams p) {
   __shared__ float red[32];
-  __shared__ int s_last;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const unsigned epoch = *reinterpret_cast<volatile unsigned*>(p.state) + 1;
 
@@ -150,24 +153,30 @@ __global__ void __launch_bounds__(1024) peer_reduce_norm_kernel(PeerReduceParams
     }
   }
 
-  // ---- 4. the last CTA to finish publishes "my rows have landed" and waits for everyone else's ----
-  __threadfence_system();
+  // ---- 4. this CTA's row has been stored everywhere: count it into every peer's "rows landed" counter ----
+  __syncthreads();
+  if ((int)blockIdx.x < p.row_count && tid < p.tp && tid != p.rank) {
+    __threadfence_system();  // the CTA's peer stores (ordered before the barrier) are performed first
+    red_add_sys(p.flags[tid] + kMaxRanks, 1u);
+  }
+  // CTA 0 waits until the rows of all peers have landed here; the kernel (and with it the stream) only
+  // moves on after that.
+  if (blockIdx.x == 0) {
+    const unsigned expected = *reinterpret_cast<volatile unsigned*>(p.state + 2) + (unsigned)(p.rows - p.row_count);
+    ok = true;
+    if (tid == 0) ok = wait_epoch(p.flags[p.rank] + kMaxRanks, expected, p.max_polls);
+    if (!__syncthreads_and(ok ? 1 : 0) && tid == 0) raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+  }
+  // The last CTA to leave advances the local state for the next call (nobody reads it any more).
   __syncthreads();
   if (tid == 0) {
-    const unsigned arrived = atomicAdd(p.state + 1, 1u);
-    s_last = arrived == gridDim.x - 1;
+    __threadfence();
+    if (atomicAdd(p.state + 1, 1u) == gridDim.x - 1) {
+      p.state[1] = 0;
+      p.state[0] = epoch;
+      p.state[2] += (unsigned)(p.rows - p.row_count);
+    }
   }
-  __syncthreads();
-  if (!s_last) return;
-  if (tid == 0) {
-    p.state[1] = 0;
-    p.state[0] = epoch;
-  }
-  __threadfence_system();
-  if (tid < p.tp && tid != p.rank) st_release_sys(p.flags[tid] + kMaxRanks + p.rank, epoch);
-  ok = true;
-  if (tid < p.tp && tid != p.rank) ok = wait_epoch(p.flags[p.rank] + kMaxRanks + tid, epoch, p.max_polls);
-  if (!__syncthreads_and(ok ? 1 : 0) && tid == 0) raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
 }
 
 typedef CUresult (*GetAddressRangeFn)(CUdeviceptr*, size_t*, CUdeviceptr);
@@ -270,6 +279,7 @@ extern "C" int mie_tp_reduce_rms_norm(const mie_tp_peers_t* peers, int32_t tp, i
   p.scale_ld = scale_ld;
   p.tp = tp;
   p.rank = rank;
+  p.rows = rows;
   p.cols = cols;
   p.row_begin = begin;
   p.row_count = end - begin;

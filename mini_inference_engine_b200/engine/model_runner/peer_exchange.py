@@ -55,7 +55,7 @@ class PeerExchange:
         if any(base % 256 for base in bases):
             raise ValueError("exchange blocks must be 256-byte aligned")
         self._bases = bases
-        self.state = torch.zeros(2, dtype=torch.int32, device=device)  # epoch, CTA arrival counter (local only)
+        self.state = torch.zeros(4, dtype=torch.int32, device=device)  # epoch, CTA arrivals, rows landed (local only)
         block = self.block
         self.partial = self._view(block, "partial", torch.bfloat16, (max_rows, cols))
         self.q = self._view(block, "q", torch.float8_e4m3fn, (max_rows, cols))
