@@ -120,3 +120,24 @@ def test_shards_are_slices_of_the_unsharded_weights():
 def test_sharded_greedy_single_rank_adds_the_offset():
     logits = torch.tensor([[0.1, 0.9, 0.3], [0.5, 0.2, 0.4]])
     assert sharded_greedy_tokens(logits, 100, 1).tolist() == [101, 100]
+
+
+def test_peer_exchange_block_layout_and_row_ownership():
+    """Host logic of the fused exchange: region offsets are aligned and disjoint, every row has one owner."""
+
+    from mini_inference_engine_b200.engine.model_runner.peer_exchange import PeerExchange
+
+    offsets, size = PeerExchange.layout(256, 2560)
+    names = ["partial", "q", "scales", "normed", "flags"]
+    assert list(offsets) == names and all(offsets[n] % 256 == 0 for n in names)
+    extents = {"partial": 256 * 2560 * 2, "q": 256 * 2560, "scales": 20 * 256 * 4, "normed": 256 * 2560 * 2, "flags": 64}
+    for first, second in zip(names, names[1:]):
+        assert offsets[first] + extents[first] <= offsets[second]
+    assert offsets["flags"] + extents["flags"] <= size
+    for tp, rows in ((2, 256), (4, 37), (8, 5), (8, 256), (3, 1)):
+        owners = []
+        for rank in range(tp):
+            ex = PeerExchange.__new__(PeerExchange)
+            ex.tp, ex.rank = tp, rank
+            owners.extend(ex.owned_rows(rows))
+        assert owners == list(range(rows))
