@@ -44,6 +44,33 @@ int cuda_fail(cudaError_t err, const char* what);
 
 int sm_count();
 void count_launch();  // every kernel launch of this library bumps a host-side counter
+bool chained_launch_enabled();  // false when MIE_PDL=0
+
+#ifdef __CUDACC__
+// Programmatic dependent launch.  A kernel launched with launch_chained() may be scheduled while the kernel
+// before it on the stream is still running; it must call chain_wait() before its first access to global
+// memory (the wait returns once the previous kernel has finished and its writes are visible) and then
+// chain_release(), which lets the kernel AFTER it be scheduled early in the same way.  Both are no-ops for
+// a kernel launched the ordinary way.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... Params, typename... Args>
+inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = chained_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+#endif
 
 // ---------------------------------------------------------------------------
 // Integer metadata views (int32 or int64, arbitrary element strides).

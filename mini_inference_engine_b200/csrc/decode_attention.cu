@@ -105,6 +105,8 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
   __shared__ int warp_tot[32];
   __shared__ int running_s;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  chain_wait();
+  chain_release();
 
   long long local = 0;
   for (int b = tid; b < batch; b += blockDim.x) local += read_length(lengths, positions, b, capacity_tokens, status);
@@ -208,6 +210,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     tma_prefetch_desc(&vmap);
   }
   __syncthreads();
+  chain_wait();
+  chain_release();
 
   const int g = lane >> 2, t = lane & 3;
   const int chunk = p.sc.header[0];
@@ -454,6 +458,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
 template <typename T, int kMergeWarpsPerHead>
 __global__ void __launch_bounds__(kMaxGroupMerge * kMergeWarpsPerHead * 32) merge_kernel(DecodeParams p) {
   __shared__ float part[kMaxGroupMerge][kMergeWarpsPerHead][2 + kHeadDim];
+  chain_wait();
+  chain_release();
   const int b = blockIdx.x / p.kv_heads, h = blockIdx.x % p.kv_heads;
   const int first = p.sc.offsets[b], n = p.sc.offsets[b + 1] - first;
   if (n <= 1) return;
@@ -686,7 +692,7 @@ int launch_fast(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMa
     MIE_CUDA(cudaFuncSetAttribute(decode_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDecodeSmem));
     configured[dev] = true;
   }
-  decode_kernel<T><<<sm_count(), kWarps * 32, kDecodeSmem, stream>>>(kmap, vmap, p);
+  MIE_CUDA(launch_chained(decode_kernel<T>, dim3(sm_count()), dim3(kWarps * 32), kDecodeSmem, stream, kmap, vmap, p));
   MIE_LAUNCH_CHECK("decode_kernel");
   // Groups wider than kMaxGroupMerge take several passes of head sub-groups.
   for (int g0 = 0; g0 < p.group; g0 += kMaxGroupMerge) {
@@ -694,9 +700,9 @@ int launch_fast(const DecodeParams& p, const CUtensorMap& kmap, const CUtensorMa
     q.merge_head0 = g0;
     const int heads = p.group - g0 < kMaxGroupMerge ? p.group - g0 : kMaxGroupMerge;
     if (p.batch >= 128)
-      merge_kernel<T, 2><<<p.batch * p.kv_heads, heads * 2 * 32, 0, stream>>>(q);
+      MIE_CUDA(launch_chained(merge_kernel<T, 2>, dim3(p.batch * p.kv_heads), dim3(heads * 2 * 32), 0, stream, q));
     else
-      merge_kernel<T, 8><<<p.batch * p.kv_heads, heads * 8 * 32, 0, stream>>>(q);
+      MIE_CUDA(launch_chained(merge_kernel<T, 8>, dim3(p.batch * p.kv_heads), dim3(heads * 8 * 32), 0, stream, q));
     MIE_LAUNCH_CHECK("merge_kernel");
   }
   return MIE_OK;

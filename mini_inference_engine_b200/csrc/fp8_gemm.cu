@@ -153,7 +153,6 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
   const int kb_first = (int)((long long)kb_total * rank / split);
   const int kb_last = (int)((long long)kb_total * (rank + 1) / split);  // exclusive
 
-  if (threadIdx.x == 0) trace_stamp(p, 0);
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       mbar_init(&full_bar[s], 1);
@@ -175,7 +174,13 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  if (threadIdx.x == 0) trace_stamp(p, 1);
+  // Barriers, tensor-map prefetch and the TMEM allocation above overlap the tail of the previous kernel.
+  chain_wait();
+  chain_release();
+  if (threadIdx.x == 0) {
+    trace_stamp(p, 0);
+    trace_stamp(p, 1);
+  }
 
   // Epilogue state that outlives the role branch (the reduction below needs it).
   constexpr int kEpiThreads = E * 32;
@@ -588,13 +593,15 @@ int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& 
   config.blockDim = dim3((E + 2) * 32, 1, 1);
   config.dynamicSmemBytes = S::kTotal;
   config.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = (unsigned)split;
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
-  config.numAttrs = 1;
+  config.numAttrs = chained_launch_enabled() ? 2 : 1;
   MIE_CUDA(cudaLaunchKernelEx(&config, fp8_gemm_kernel<BN, E, kSwap>, mr, mc, p));
   MIE_LAUNCH_CHECK("fp8_gemm_kernel");
   return MIE_OK;

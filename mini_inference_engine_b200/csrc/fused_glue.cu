@@ -31,6 +31,8 @@ struct RowNormParams {
 
 __global__ void __launch_bounds__(1024) row_norm_kernel(RowNormParams p) {
   __shared__ float red[32];
+  chain_wait();
+  chain_release();
   const int row = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int c0 = tid * 8;
@@ -102,6 +104,8 @@ __global__ void head_norm_kernel(const __nv_bfloat16* x, long long outer_stride,
 __global__ void silu_mul_kernel(const __nv_bfloat16* gate, const __nv_bfloat16* up, long long ld_in,
                                 __nv_bfloat16* out, uint8_t* q, long long ldq, float* scales, int scale_ld,
                                 int rows, int cols) {
+  chain_wait();
+  chain_release();
   const int per_row = cols / 8;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const bool live = idx < (long long)rows * per_row;
@@ -176,6 +180,8 @@ struct QkvParams {
 };
 
 __global__ void qkv_post_kernel(QkvParams p) {
+  chain_wait();
+  chain_release();
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   const int heads_total = p.q_heads + 2 * p.kv_heads;
@@ -269,7 +275,7 @@ extern "C" int mie_rms_norm(const void* x, int64_t ldx, const void* residual, vo
                   (const __nv_bfloat16*)weight, (__nv_bfloat16*)out, (uint8_t*)q, ldq, scales, scale_ld, rows, cols,
                   eps};
   const int threads = ((cols / 8) + 31) / 32 * 32;
-  row_norm_kernel<<<rows, threads, 0, (cudaStream_t)stream>>>(p);
+  MIE_CUDA(launch_chained(row_norm_kernel, dim3(rows), dim3(threads), 0, (cudaStream_t)stream, p));
   MIE_LAUNCH_CHECK("row_norm_kernel");
   return MIE_OK;
 }
@@ -299,9 +305,10 @@ extern "C" int mie_silu_mul(const void* gate, const void* up, int64_t ld_in, voi
   if (rows == 0) return MIE_OK;
   const long long work = (long long)rows * (cols / 8);
   const int threads = 256;
-  silu_mul_kernel<<<(unsigned)((work + threads - 1) / threads), threads, 0, (cudaStream_t)stream>>>(
+  MIE_CUDA(launch_chained(silu_mul_kernel, dim3((unsigned)((work + threads - 1) / threads)), dim3(threads), 0,
+                          (cudaStream_t)stream,
       (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, ld_in, (__nv_bfloat16*)out, (uint8_t*)q, ldq, scales,
-      scale_ld, rows, cols);
+      scale_ld, rows, cols));
   MIE_LAUNCH_CHECK("silu_mul_kernel");
   return MIE_OK;
 }
@@ -368,7 +375,8 @@ extern "C" int mie_qkv_norm_rope_write(const void* qkv, int64_t ld, const void* 
   p.status = status;
   const long long warps = (long long)tokens * (q_heads + 2 * kv_heads);
   const int threads = 256;
-  qkv_post_kernel<<<(unsigned)((warps * 32 + threads - 1) / threads), threads, 0, (cudaStream_t)stream>>>(p);
+  MIE_CUDA(launch_chained(qkv_post_kernel, dim3((unsigned)((warps * 32 + threads - 1) / threads)), dim3(threads), 0,
+                          (cudaStream_t)stream, p));
   MIE_LAUNCH_CHECK("qkv_post_kernel");
   return MIE_OK;
 }

@@ -79,6 +79,8 @@ __device__ __forceinline__ void red_add_sys(unsigned* p, unsigned v) {
 __global__ void __launch_bounds__(1024) peer_reduce_norm_kernel(PeerReduceParams p) {
   __shared__ float red[32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  chain_wait();  // the projection before this kernel has finished: its partial sums are complete
+  chain_release();
   const unsigned epoch = *reinterpret_cast<volatile unsigned*>(p.state) + 1;
 
   // ---- 1. my partial sums are complete (this kernel follows the GEMM in stream order); wait for the peers' ----
@@ -288,7 +290,7 @@ extern "C" int mie_tp_reduce_rms_norm(const mie_tp_peers_t* peers, int32_t tp, i
   p.max_polls = max_polls == 0 ? (1u << 22) : max_polls;
   const int threads = ((cols / 8) + 31) / 32 * 32;
   const int blocks = p.row_count > 0 ? p.row_count : 1;  // a rank without rows still takes part in both waits
-  peer_reduce_norm_kernel<<<blocks, threads, 0, (cudaStream_t)stream>>>(p);
+  MIE_CUDA(launch_chained(peer_reduce_norm_kernel, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, p));
   MIE_LAUNCH_CHECK("peer_reduce_norm_kernel");
   return MIE_OK;
 }

@@ -1,6 +1,7 @@
 // Host-side runtime support: error strings, device queries, tensor-map encoding.
 #include <stdarg.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include <atomic>
 #include <mutex>
@@ -25,6 +26,14 @@ int cuda_fail(cudaError_t err, const char* what) {
 
 static std::atomic<long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+bool chained_launch_enabled() {
+  static const bool enabled = [] {
+    const char* v = getenv("MIE_PDL");
+    return !(v != nullptr && v[0] == '0');
+  }();
+  return enabled;
+}
 
 int sm_count() {
   static int cached[64] = {0};
