@@ -161,6 +161,7 @@ class DecodeBuffers:
 
     def __init__(self, batch: int, table_width: int, device: torch.device) -> None:
         self.batch, self.table_width = batch, table_width
+        self.advance = False  # True when the captured graph feeds its tokens back and bumps the lengths
         self.input_ids = torch.zeros(batch, dtype=torch.int64, device=device)
         self.sequence_lengths = torch.ones(batch, dtype=torch.int32, device=device)
         self.block_tables = torch.zeros(batch, table_width, dtype=torch.int32, device=device)
@@ -438,18 +439,25 @@ class Qwen3DecodeRunner:
         cu = torch.zeros(batch + 1, dtype=torch.int32)
         cu[1:] = torch.tensor(lengths, dtype=torch.int32).cumsum(0)
         kv_lens = torch.tensor(lengths, dtype=torch.int32, device=device)
+        buffers = None
+        if use_graph and max_new_tokens > 1:
+            # A graph captured for this batch size and table width by an earlier call is reused (a serving
+            # engine captures once at start-up).  Capture runs throw-away steps that write position 0 of page
+            # 0, so it happens before the prompt is written.
+            cached = self._graphs.get(batch)
+            if cached is not None and cached[1].advance and cached[1].block_tables.shape[1] == width:
+                buffers = cached[1]
+            else:
+                buffers = self.capture(batch, width, advance=True)
         next_ids = self.prefill_forward(flat, tok2seq, tokpos, tables_dev, cu.to(device), kv_lens, max(lengths))
         outputs = [[int(t)] for t in next_ids.tolist()]
         current = kv_lens.clone()
-        if use_graph and max_new_tokens > 1:
-            buffers = self.capture(batch, width, advance=True)
-            # Capture runs throw-away steps that write position 0 of page 0: restore it from the prompt.
-            self.prefill_forward(flat, tok2seq, tokpos, tables_dev, cu.to(device), kv_lens, max(lengths))
+        if buffers is not None:
             buffers.input_ids.copy_(next_ids)
             buffers.block_tables.copy_(tables_dev)
             buffers.sequence_lengths.copy_(current + 1)
         for _ in range(max_new_tokens - 1):
-            if use_graph:
+            if buffers is not None:
                 self.replay(batch)
                 next_ids = buffers.output_tokens.clone()
             else:
@@ -467,6 +475,7 @@ class Qwen3DecodeRunner:
         sampled tokens back as the next inputs and bumps the lengths, so replays need no host work."""
 
         buffers = DecodeBuffers(batch, table_width, self.device)
+        buffers.advance = advance
         side = torch.cuda.Stream(device=self.device)
         side.wait_stream(torch.cuda.current_stream(self.device))
         with torch.cuda.stream(side):
