@@ -232,6 +232,7 @@ def run_config3(args, shape, device, rank, world, group) -> None:
         print(json.dumps({
             "metric": "output tok/s, 8 requests x 2048-token prompts, 128 new tokens (configuration 3)",
             "value": requests * new_tokens / wall, "unit": "tok/s", "n_gpus": world, "seconds": wall,
+            "vs_baseline": requests * new_tokens / wall / 160.6,  # the reference's published L4 number
             "higher_is_better": True, "data": "synthetic", "dtype": "fp8_e4m3 GEMM / bf16 KV+activations",
             "config": {"workload": "config3", "requests": requests, "prompt_tokens": prompt_len,
                        "new_tokens": new_tokens, "includes": "packed prefill + 127 graph decode steps (the graph was captured by the warm-up generation)"},
