@@ -255,11 +255,13 @@ int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t
  * x8 [m, k] e4m3 (row stride ldx bytes), a_scale as mie_fp8_quantize writes it,
  * w8 [n, k] e4m3 (row stride ldw bytes), w_scale [ceil(n/128), w_scale_ld].
  * Operand base pointers and row strides must be multiples of 16 bytes.
- * When a shape has fewer output tiles than SMs the K range of each tile is cut
- * into up to 8 parts that run as one thread-block cluster and are summed in a
- * fixed order through distributed shared memory; max_split > 0 caps that
- * factor (1 = never split), 0 lets the library choose.  trace is a profiling
- * aid: NULL, or a device buffer of 16 int64 per CTA that receives %globaltimer
+ * Up to 128 tokens run with the weight rows as the 128 MMA rows (a weight
+ * streaming loop); more tokens run a persistent 128 x 256-tile kernel.  When a
+ * shape has fewer output tiles than SMs the K range of each tile is cut into
+ * 2 or 4 parts that run as one thread-block cluster and are summed in a fixed
+ * order through distributed shared memory; max_split > 0 caps that factor
+ * (1 = never split), 0 lets the library choose.  trace is a profiling aid:
+ * NULL, or a device buffer of 16 int64 per CTA that receives %globaltimer
  * stamps of the kernel's phases.  Uses no global scratch memory.
  */
 int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,

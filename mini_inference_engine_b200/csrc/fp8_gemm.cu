@@ -8,23 +8,19 @@
 //     memory by TMA (2-D tiled loads, 128-byte swizzle, no multicast), fp32
 //     accumulators in tensor memory.
 //   * The scales change every 128 columns of K, so each K block is accumulated
-//     in its own TMEM buffer (two buffers, ping-pong) and the epilogue warps
-//     promote it into fp32 registers with that block's scale (tcgen05.ld +
-//     FFMA) while the tensor core already works on the next block.
-//   * Warp roles: E epilogue warps (E = 4 or 8), one TMA producer warp, one
-//     MMA-issuer warp that also owns the TMEM allocation.
-//   * Two orientations share the kernel.  "Normal" (many tokens): the 128 UMMA
-//     rows are tokens, the BN columns are weight rows.  "Swapped" (few tokens,
-//     decode): the 128 UMMA rows are weight rows and the BN columns are tokens,
-//     so a handful of tokens still fills the tensor core's M and the kernel is
-//     a pure weight-streaming (HBM-bound) loop.
-//   * Schedule: grid = (tiles, split).  When a shape has fewer output tiles
-//     than SMs (decode), the K range of every tile is cut into `split` (<= 8)
-//     parts that run as one thread-block cluster; each CTA parks its fp32
-//     partial in its own shared memory and, after a cluster barrier, reduces a
-//     slice of the tile by reading its peers through distributed shared
-//     memory in a fixed order (deterministic; no global partials, no atomics,
-//     no spinning).  With enough tiles split = 1 and CTAs store directly.
+//     in its own TMEM buffer (a ring) and the promotion warps add it into fp32
+//     registers with that block's scale (tcgen05.ld + FFMA) while the tensor
+//     core already works on the next block.
+//   * Two kernels.  Up to 128 tokens (decode): fp8_gemm_kernel, "swapped" - the
+//     128 UMMA rows are weight rows and the BN = 16..128 columns are tokens, so
+//     a handful of tokens still fills the tensor core's M and the kernel is a
+//     pure weight-streaming (HBM-bound) loop; E = 4 promotion warps, one TMA
+//     producer warp, one MMA-issuer warp that also owns the TMEM allocation.
+//     More than 128 tokens: fp8_gemm_wide_kernel (described at its definition).
+//   * A shape with fewer output tiles than SMs cuts the K range of every tile
+//     into parts that run as one thread-block cluster and are reduced through
+//     distributed shared memory in a fixed order (deterministic; no global
+//     partials, no atomics, no spinning).
 //   * Every mbarrier wait is bounded; a wait that runs out sets
 //     MIE_STATUS_WAIT_TIMEOUT, the roles fall through to the common exit and
 //     TMEM is released.
@@ -456,6 +452,430 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
 }
 
 // --------------------------------------------------------------------------
+// Wide kernel (more than 128 tokens): tokens are the 128 UMMA rows, 256 weight rows the columns.
+//
+//   * Schedule, grid = (CTAs, split).  With at least as many tiles as SMs the grid is persistent (split =
+//     1, one CTA per SM): CTA c takes tiles c, c + P, c + 2P, ... whole and stores a finished tile while
+//     the tensor core already works on the next one.  A shape with fewer tiles than SMs runs one tile per
+//     2- or 4-CTA cluster, each CTA taking a slice of K: every CTA parks its fp32 partial in its own (then
+//     idle) stage ring in a swizzled [row][4-column group] layout, and after a cluster barrier reads the
+//     column slice it owns from every peer with 16-byte distributed-shared-memory loads, adds the partials
+//     in rank order (a fixed order: results do not depend on timing) and stores bf16.  No global scratch.
+//   * 12 warps: 8 promotion warps (two warpgroups), one TMA producer, one MMA issuer, two idle.  The
+//     producer warpgroup hands most of its registers to the promotion warps (setmaxnreg), which keep the
+//     128 x 256 fp32 result in registers (128 per thread) next to two 32-column landing buffers.
+//   * Two 256-column accumulators ping-pong in TMEM.  Promotion of one K block: two rounds of two TMEM loads
+//     in flight; the multiply-adds (packed fp32x2) of one landing buffer run while the other is being
+//     refilled, and the first loads of the next K block are issued before the last columns of the current
+//     one are consumed.  The accumulator goes back to the MMA issuer as soon as its last load has landed.
+// --------------------------------------------------------------------------
+constexpr int kWideBN = 256;
+constexpr int kWideEpiWarps = 8;
+constexpr int kWideThreads = 384;
+constexpr int kWideStages = 4;
+constexpr int kWideStageBytes = kTileR * kBlockK + kWideBN * kBlockK;  // 48 KiB
+constexpr int kWideChunkKb = 16;                                        // K blocks of scales staged at a time
+constexpr int kWideScaleFloats = kWideChunkKb * (kTileR + 2);
+constexpr int kWideStoreBytes = kWideEpiWarps * 2048;  // per promotion warp: 32 rows x 32 columns of 16-bit output
+constexpr int kWideSmemBytes = kWideStages * kWideStageBytes + kWideStoreBytes + (2 * kWideStages + 4) * 8 +
+                               kWideScaleFloats * 4 + 64 + 1024;
+static_assert(kWideStages * kWideStageBytes >= kTileR * kWideBN * 4, "stage ring too small for the fp32 partial tile");
+
+struct WideItem {
+  int tm, tn, k0, k1;
+};
+
+// Work of CTA (x, rank) of a (gridDim.x, split) grid.  split == 1: tiles x, x + gridDim.x, ... whole.
+// split > 1 (one cluster per tile): tile x, the rank-th part of its K range.
+__device__ __forceinline__ bool wide_item(int tiles, int tiles_m, int kb_total, int split, int rank, int idx,
+                                          WideItem& it) {
+  const int tile = blockIdx.x + idx * gridDim.x;
+  if (tile >= tiles || (split > 1 && idx > 0)) return false;
+  it.tm = tile % tiles_m;
+  it.tn = tile / tiles_m;
+  it.k0 = (int)((long long)kb_total * rank / split);
+  it.k1 = (int)((long long)kb_total * (rank + 1) / split);
+  return true;
+}
+
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t local_addr, uint32_t rank) {
+  uint32_t remote;
+  float4 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(remote)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void tmem_ld_wait_pin(float (&a)[32], float (&b)[32]) {
+  // The wait is what makes the registers of the earlier tcgen05.ld valid; naming them as in/out operands
+  // keeps every later use of a and b behind it.
+  uint32_t* r = reinterpret_cast<uint32_t*>(a);
+  uint32_t* q = reinterpret_cast<uint32_t*>(b);
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                 "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]),
+                 "+r"(r[15]), "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]),
+                 "+r"(r[22]), "+r"(r[23]), "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]),
+                 "+r"(r[29]), "+r"(r[30]), "+r"(r[31]), "+r"(q[0]), "+r"(q[1]), "+r"(q[2]), "+r"(q[3]), "+r"(q[4]),
+                 "+r"(q[5]), "+r"(q[6]), "+r"(q[7]), "+r"(q[8]), "+r"(q[9]), "+r"(q[10]), "+r"(q[11]),
+                 "+r"(q[12]), "+r"(q[13]), "+r"(q[14]), "+r"(q[15]), "+r"(q[16]), "+r"(q[17]), "+r"(q[18]),
+                 "+r"(q[19]), "+r"(q[20]), "+r"(q[21]), "+r"(q[22]), "+r"(q[23]), "+r"(q[24]), "+r"(q[25]),
+                 "+r"(q[26]), "+r"(q[27]), "+r"(q[28]), "+r"(q[29]), "+r"(q[30]), "+r"(q[31])
+               :
+               : "memory");
+}
+
+// acc[0..32) += d[0..32) * s, two columns per instruction.
+__device__ __forceinline__ void promote32(float* acc, const float (&d)[32], float s) {
+  const float2 s2 = make_float2(s, s);
+#pragma unroll
+  for (int j = 0; j < 32; j += 2) {
+    const float2 r = __ffma2_rn(make_float2(d[j], d[j + 1]), s2, make_float2(acc[j], acc[j + 1]));
+    acc[j] = r.x;
+    acc[j + 1] = r.y;
+  }
+}
+
+__device__ __forceinline__ void wide_stamp(const GemmParams& p, int slot) {
+  if (p.trace != nullptr) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    p.trace[(size_t)(blockIdx.x * gridDim.y + blockIdx.y) * 16 + slot] = (long long)t;
+  }
+}
+
+__global__ void __launch_bounds__(kWideThreads, 1)
+    fp8_gemm_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                         const GemmParams p) {
+  constexpr int BN = kWideBN, E = kWideEpiWarps, kStages = kWideStages, kAcc = 2;
+  constexpr int kCols = BN / 2;  // columns owned by one promotion warp
+  constexpr uint32_t kTmemCols = 512;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage_base = smem;
+  uint8_t* store_base = smem + kStages * kWideStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(store_base + kWideStoreBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint64_t* tmem_empty = tmem_full + kAcc;
+  float* sscale = reinterpret_cast<float*>(tmem_empty + kAcc);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sscale + kWideScaleFloats);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_total = (p.k + kBlockK - 1) / kBlockK;
+  const int tiles_m = (p.m + kTileR - 1) / kTileR;
+  const int tiles = tiles_m * ((p.n + BN - 1) / BN);
+  const int split = gridDim.y, rank = blockIdx.y;  // cluster = (1, split, 1)
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < kAcc; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], E);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&map_x);
+    tma_prefetch_desc(&map_w);
+  }
+  if (warp == E + 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // Barriers, tensor-map prefetch and the TMEM allocation above overlap the tail of the previous kernel.
+  chain_wait();
+  chain_release();
+  if (threadIdx.x == 0) wide_stamp(p, 0);
+
+  // K blocks this CTA will process (the promotion pipeline needs to know when the last one is reached).
+  uint32_t total_blocks = 0;
+  {
+    WideItem it;
+    for (int idx = 0; wide_item(tiles, tiles_m, kb_total, split, rank, idx, it); ++idx) total_blocks += (uint32_t)(it.k1 - it.k0);
+  }
+
+  if (warp >= E) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+    if (warp == E && lane == 0) {
+      // ---------------- TMA producer ----------------
+      uint32_t n = 0;
+      bool ok = true;
+      WideItem it;
+      for (int idx = 0; ok && wide_item(tiles, tiles_m, kb_total, split, rank, idx, it); ++idx) {
+        for (int kb = it.k0; kb < it.k1; ++kb, ++n) {
+          const int s = n % kStages;
+          if (!mbar_wait_bounded(&empty_bar[s], ((n / kStages) & 1u) ^ 1u)) {
+            raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+            ok = false;
+            break;
+          }
+          uint8_t* dst = stage_base + (size_t)s * kWideStageBytes;
+          mbar_expect_tx(&full_bar[s], kWideStageBytes);
+          tma_load_2d(dst, &map_x, &full_bar[s], kb * kBlockK, it.tm * kTileR);
+          tma_load_2d(dst + kTileR * kBlockK, &map_w, &full_bar[s], kb * kBlockK, it.tn * BN);
+        }
+      }
+    } else if (warp == E + 1 && lane == 0) {
+      // ---------------- MMA issuer ----------------
+      constexpr uint32_t idesc = instr_desc_f8(BN);
+      for (uint32_t n = 0; n < total_blocks; ++n) {
+        const int s = n % kStages, b = n % kAcc;
+        if (!mbar_wait_bounded(&full_bar[s], (n / kStages) & 1u) ||
+            !mbar_wait_bounded(&tmem_empty[b], ((n / kAcc) & 1u) ^ 1u)) {
+          raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(stage_base + (size_t)s * kWideStageBytes);
+        const uint64_t da = smem_desc_k128(a_addr), db = smem_desc_k128(a_addr + kTileR * kBlockK);
+#pragma unroll
+        for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+          umma_f8(tmem_base + b * BN, da + (uint64_t)(k * kUmmaK / 16), db + (uint64_t)(k * kUmmaK / 16), idesc,
+                  k > 0 ? 1u : 0u);
+        }
+        umma_commit(&empty_bar[s]);  // frees the smem stage once these MMAs have read it
+        umma_commit(&tmem_full[b]);  // hands the K block's accumulator to the promotion warps
+      }
+    }
+    __syncwarp();
+    if (split > 1) {
+      cluster_sync_all();  // partials parked
+      cluster_sync_all();  // peers have read this CTA's partial
+    }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+    // ---------------- Promotion warps ----------------
+    constexpr int kEpiThreads = E * 32;
+    const int quad = warp & 3, half = warp >> 2;
+    const int row_in_tile = quad * 32 + lane;
+    const int col0 = half * kCols;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)col0;
+    const int epi_tid = threadIdx.x;
+    float acc[kCols];
+    float buf_a[32], buf_b[32];
+#pragma unroll
+    for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+    uint32_t n = 0;
+    bool ok = true;
+    // First accumulator: its first 64 columns start the pipeline.
+    if (total_blocks > 0) {
+      ok = mbar_wait_bounded(&tmem_full[0], 0);
+      if (!ok) raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+      tc_fence_after();
+      if (ok) {
+        tmem_ld32(lane_addr, buf_a);
+        tmem_ld32(lane_addr + 32, buf_b);
+      }
+      if (epi_tid == 0) wide_stamp(p, 1);
+    }
+    WideItem it;
+    for (int idx = 0; ok && wide_item(tiles, tiles_m, kb_total, split, rank, idx, it); ++idx) {
+      const int tok0 = it.tm * kTileR;
+      for (int kb0 = it.k0; kb0 < it.k1 && ok; kb0 += kWideChunkKb) {
+        const int kc = it.k1 - kb0 < kWideChunkKb ? it.k1 - kb0 : kWideChunkKb;
+        // Stage this chunk's scales (all loads in flight together).
+        epi_bar_sync(kEpiThreads);  // the previous chunk's readers are done
+        float* s_w = sscale + kWideChunkKb * kTileR;
+        for (int i = epi_tid; i < kc * kTileR; i += kEpiThreads) {
+          const int kk = i / kTileR, tok = tok0 + i % kTileR;
+          sscale[i] = tok < p.m ? p.a_scale[(long long)(kb0 + kk) * p.a_scale_ld + tok] : 0.f;
+        }
+        for (int i = epi_tid; i < kc * 2; i += kEpiThreads) {
+          const int kk = i >> 1, blk = it.tn * 2 + (i & 1);
+          s_w[i] = blk * 128 < p.n ? p.w_scale[(long long)blk * p.w_scale_ld + kb0 + kk] : 0.f;
+        }
+        epi_bar_sync(kEpiThreads);
+        for (int kk = 0; kk < kc; ++kk, ++n) {
+          const int b = n & 1;
+          const float s = sscale[kk * kTileR + row_in_tile] * s_w[kk * 2 + half];
+          const uint32_t taddr = lane_addr + (uint32_t)(b * BN);
+          tmem_ld_wait_pin(buf_a, buf_b);  // columns 0..63 have landed
+          promote32(acc, buf_a, s);
+          tmem_ld32(taddr + 64, buf_a);
+          promote32(acc + 32, buf_b, s);
+          tmem_ld32(taddr + 96, buf_b);
+          tmem_ld_wait_pin(buf_a, buf_b);  // columns 64..127 have landed
+          // Every load of this accumulator has landed: hand the buffer back to the MMA issuer.
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&tmem_empty[b]);
+          promote32(acc + 64, buf_a, s);
+          const bool more = n + 1 < total_blocks;
+          if (more) {
+            if (!mbar_wait_bounded(&tmem_full[b ^ 1], ((n + 1) >> 1) & 1u)) {
+              raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+              ok = false;
+            }
+            tc_fence_after();
+            if (ok) tmem_ld32(lane_addr + (uint32_t)((b ^ 1) * BN), buf_a);
+          }
+          promote32(acc + 96, buf_b, s);
+          if (more && ok) tmem_ld32(lane_addr + (uint32_t)((b ^ 1) * BN) + 32, buf_b);
+          if (!ok) break;
+        }
+      }
+      if (!ok) break;
+      if (epi_tid == 0) wide_stamp(p, 2);
+
+      const int r_glob = tok0 + row_in_tile;
+      if (split == 1) {
+        const int n0 = it.tn * BN + col0;
+        const bool vec = (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) && (n0 + kCols <= p.n);
+        if (vec) {
+          // Rows leave through a per-warp staging area so that global stores are whole 64-byte row
+          // segments: a lane parks 32 columns of its own row (4 x 16 bytes, unit u of row r at
+          // r * 4 + ((u + r / 2) & 3): conflict-free both ways), then four lanes store one row segment.
+          uint4* stage = reinterpret_cast<uint4*>(store_base + warp * 2048);
+          const int out_row = lane >> 2, unit = lane & 3;
+#pragma unroll
+          for (int c = 0; c < kCols; c += 32) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              uint32_t w[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int j = c + u * 8 + 2 * q;
+                w[q] = p.out_f16 ? Mma16816<__half>::pack(acc[j], acc[j + 1])
+                                 : Mma16816<__nv_bfloat16>::pack(acc[j], acc[j + 1]);
+              }
+              stage[lane * 4 + ((u + (lane >> 1)) & 3)] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int r8 = 0; r8 < 32; r8 += 8) {
+              const int r = r8 + out_row;
+              const uint4 v = stage[r * 4 + ((unit + (r >> 1)) & 3)];
+              const int tok = tok0 + quad * 32 + r;
+              if (tok < p.m) {
+                uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + (long long)tok * p.ldy + n0 + c + unit * 8;
+                *reinterpret_cast<uint4*>(dst) = v;
+              }
+            }
+            __syncwarp();
+          }
+        } else if (r_glob < p.m) {
+          uint16_t* yrow = reinterpret_cast<uint16_t*>(p.y) + (long long)r_glob * p.ldy + n0;
+#pragma unroll
+          for (int j = 0; j < kCols; ++j) {
+            if (n0 + j < p.n) {
+              if (p.out_f16)
+                reinterpret_cast<__half*>(yrow)[j] = __float2half_rn(acc[j]);
+              else
+                reinterpret_cast<__nv_bfloat16*>(yrow)[j] = __float2bfloat16_rn(acc[j]);
+            }
+          }
+        }
+      } else {
+        // Park the partial: float4 (row, g) lives at slot row * 64 + (g ^ (row & 7)), so that both the
+        // row-per-lane writes here and the column-group-per-lane reads below are free of bank conflicts.
+        // Every MMA of this CTA has completed (its last accumulator was consumed), so the ring is idle.
+        float4* park = reinterpret_cast<float4*>(stage_base);
+#pragma unroll
+        for (int j = 0; j < kCols; j += 4) {
+          const int g = (col0 + j) >> 2;
+          park[row_in_tile * 64 + (g ^ (row_in_tile & 7))] = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        }
+        if (epi_tid == 0) wide_stamp(p, 3);
+        cluster_sync_all();
+        // This CTA adds the 4-column groups [g_lo, g_hi) of the tile's 64 over all ranks, in rank order.
+        const int g_lo = 64 * rank / split, g_hi = 64 * (rank + 1) / split, groups = g_hi - g_lo;
+        const uint32_t park_addr = smem_u32(stage_base);
+        const bool vec = (p.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 7) == 0);
+        // Two (row, group) items per thread at a time, every peer's load of both in flight together.
+        for (int i0 = epi_tid; i0 < kTileR * groups; i0 += 2 * kEpiThreads) {
+          float4 part[2][4];
+          uint32_t slot[2];
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int i = i0 + u * kEpiThreads;
+            const int row = i / groups, g = g_lo + i % groups;
+            slot[u] = park_addr + (uint32_t)((row * 64 + (g ^ (row & 7))) * 16);
+          }
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            if (i0 + u * kEpiThreads < kTileR * groups) {
+#pragma unroll
+              for (int peer = 0; peer < 4; ++peer)
+                if (peer < split) part[u][peer] = ld_cluster_f4(slot[u], (uint32_t)peer);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int i = i0 + u * kEpiThreads;
+            if (i >= kTileR * groups) continue;
+            const int row = i / groups, g = g_lo + i % groups;
+            float4 sum = part[u][0];
+#pragma unroll
+            for (int peer = 1; peer < 4; ++peer) {
+              if (peer < split) {
+                sum.x += part[u][peer].x;
+                sum.y += part[u][peer].y;
+                sum.z += part[u][peer].z;
+                sum.w += part[u][peer].w;
+              }
+            }
+            const int tok = tok0 + row, n0 = it.tn * BN + g * 4;
+            if (tok < p.m && n0 < p.n) {
+              uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + (long long)tok * p.ldy + n0;
+              if (vec && n0 + 4 <= p.n) {
+                uint2 w;
+                w.x = p.out_f16 ? Mma16816<__half>::pack(sum.x, sum.y) : Mma16816<__nv_bfloat16>::pack(sum.x, sum.y);
+                w.y = p.out_f16 ? Mma16816<__half>::pack(sum.z, sum.w) : Mma16816<__nv_bfloat16>::pack(sum.z, sum.w);
+                *reinterpret_cast<uint2*>(dst) = w;
+              } else {
+                const float v[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (n0 + j < p.n) {
+                    if (p.out_f16)
+                      reinterpret_cast<__half*>(dst)[j] = __float2half_rn(v[j]);
+                    else
+                      reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(v[j]);
+                  }
+                }
+              }
+            }
+          }
+        }
+        if (epi_tid == 0) wide_stamp(p, 4);
+        cluster_sync_all();  // no CTA leaves while a peer may still read its partial
+      }
+      if (epi_tid == 0) wide_stamp(p, 5);
+#pragma unroll
+      for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+    }
+    if (!ok) {
+      tmem_ld_wait();  // nothing of this thread stays in flight
+      if (split > 1) {  // a CTA that gave up still meets its peers at the two cluster barriers
+        cluster_sync_all();
+        cluster_sync_all();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == E + 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0) {
+    if (p.trace != nullptr) p.trace[(size_t)(blockIdx.x * gridDim.y + blockIdx.y) * 16 + 7] = (long long)total_blocks;
+    wide_stamp(p, 6);
+  }
+}
+
+// --------------------------------------------------------------------------
 // Activation quantiser: per token, per 128 columns.  One half-warp per group.
 // --------------------------------------------------------------------------
 template <typename T>
@@ -610,6 +1030,60 @@ int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& 
 // Column-tile width for the swapped orientation: smallest of 16/32/64/128 covering m.
 int swap_bn(int m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
 
+// Schedule of the wide kernel for `tiles` output tiles of `kb` K blocks: persistent whole tiles (split 1)
+// or one tile per `split`-CTA cluster.  Costs in units of one K block of the main loop; the cluster
+// reduction and the fill / drain of a CTA are worth a few blocks each.
+int choose_wide_split(long long tiles, int kb, int max_split) {
+  const int slots = sm_count();
+  int best = 1;
+  double best_cost = 1e30;
+  for (int s = 1; s <= 4; s *= 2) {
+    if (s > kb || (max_split > 0 && s > max_split)) break;
+    if (s > 1 && tiles * s > slots) break;  // clusters only when all of them run in one wave
+    const double rounds = (double)((tiles * s + slots - 1) / slots);
+    const double cost = rounds * ((kb + s - 1) / s) + 4.0 + (s > 1 ? 3.0 : 0.0);
+    if (cost < best_cost - 1e-9) {
+      best_cost = cost;
+      best = s;
+    }
+  }
+  return best;
+}
+
+int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, const GemmParams& p, int max_split,
+                cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  MIE_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    MIE_CUDA(cudaFuncSetAttribute(fp8_gemm_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kWideSmemBytes));
+    configured[dev] = true;
+  }
+  const int kb = (p.k + kBlockK - 1) / kBlockK;
+  const long long tiles = (long long)((p.m + kTileR - 1) / kTileR) * ((p.n + kWideBN - 1) / kWideBN);
+  MIE_CHECK_ARG(tiles <= 0x7fffffff, "too many output tiles (%lld)", tiles);
+  const int split = choose_wide_split(tiles, kb, max_split);
+  const long long ctas = split > 1 ? tiles : (tiles < sm_count() ? tiles : sm_count());
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((unsigned)ctas, (unsigned)split, 1);
+  config.blockDim = dim3(kWideThreads, 1, 1);
+  config.dynamicSmemBytes = kWideSmemBytes;
+  config.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = (unsigned)split;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attr;
+  config.numAttrs = chained_launch_enabled() ? 2 : 1;
+  MIE_CUDA(cudaLaunchKernelEx(&config, fp8_gemm_wide_kernel, mx, mw, p));
+  MIE_LAUNCH_CHECK("fp8_gemm_wide_kernel");
+  return MIE_OK;
+}
+
 }  // namespace
 }  // namespace mie
 
@@ -685,6 +1159,6 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
     }
   }
   if (int rc = operand_map(x8, m, k, ldx, kTileR, &mr)) return rc;
-  if (int rc = operand_map(w8, n, k, ldw, bn, &mc)) return rc;
-  return launch_gemm<256, 8, false>(mr, mc, p, tiles, split, stream);
+  if (int rc = operand_map(w8, n, k, ldw, kWideBN, &mc)) return rc;
+  return launch_wide(mr, mc, p, max_split, stream);
 }
