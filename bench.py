@@ -345,7 +345,10 @@ def main() -> None:
     e2e = None
     if e2e_steps:
         runner.capture(concurrency, width, advance=False)
-        host_lengths = (contexts + 1 + grown).to(torch.int32)
+        # Same workload as the device-resident loop: every context starts again at its drawn length (the
+        # pool's contents are random either way), so the two numbers differ only by the host round trip.
+        grown = 0
+        host_lengths = (contexts + 1).to(torch.int32)
         host_ids = buffers.output_tokens.cpu()
         for _ in range(warmup):
             host_ids, _, _ = runner.step_host(concurrency, host_ids, host_lengths, tables)
@@ -364,7 +367,7 @@ def main() -> None:
         runner.check_status()
         e2e = {"value": concurrency * e2e_steps / wall, "unit": "tok/s", "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": wall / e2e_steps * 1e3}
-        grown += warmup + e2e_steps
+        grown = warmup + e2e_steps
 
     # ---- roofline of the dominant kernel: paged decode attention, timed alone with CUDA events ----
     lengths_now = (contexts + 1 + grown).to(torch.int32).to(device)

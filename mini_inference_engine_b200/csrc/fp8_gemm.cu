@@ -547,6 +547,60 @@ __device__ __forceinline__ void wide_stamp(const GemmParams& p, int slot) {
   }
 }
 
+// Cluster reduction of a K-split tile: this CTA adds the 4-column groups [g_lo, g_lo + 64 / kSplit) of the
+// tile over all ranks, in rank order, and stores them.  A thread owns 32 / kSplit (row, group) items and has
+// the loads of all of them, from every rank, in flight together (one exposed round trip instead of many).
+template <int kSplit>
+__device__ __forceinline__ void wide_cluster_reduce(const GemmParams& p, uint32_t park_addr, int rank, int epi_tid,
+                                                    int tok0, int col_base) {
+  constexpr int kGroups = 64 / kSplit, kItems = kTileR * kGroups / (kWideEpiWarps * 32);
+  const int g_lo = kGroups * rank;
+  const bool vec = (p.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 7) == 0);
+  float4 part[kItems][kSplit];
+#pragma unroll
+  for (int u = 0; u < kItems; ++u) {
+    const int i = epi_tid + u * (kWideEpiWarps * 32);
+    const int row = i / kGroups, g = g_lo + i % kGroups;
+    const uint32_t slot = park_addr + (uint32_t)((row * 64 + (g ^ (row & 7))) * 16);
+#pragma unroll
+    for (int peer = 0; peer < kSplit; ++peer) part[u][peer] = ld_cluster_f4(slot, (uint32_t)peer);
+  }
+#pragma unroll
+  for (int u = 0; u < kItems; ++u) {
+    const int i = epi_tid + u * (kWideEpiWarps * 32);
+    const int row = i / kGroups, g = g_lo + i % kGroups;
+    float4 sum = part[u][0];
+#pragma unroll
+    for (int peer = 1; peer < kSplit; ++peer) {
+      sum.x += part[u][peer].x;
+      sum.y += part[u][peer].y;
+      sum.z += part[u][peer].z;
+      sum.w += part[u][peer].w;
+    }
+    const int tok = tok0 + row, n0 = col_base + g * 4;
+    if (tok < p.m && n0 < p.n) {
+      uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + (long long)tok * p.ldy + n0;
+      if (vec && n0 + 4 <= p.n) {
+        uint2 w;
+        w.x = p.out_f16 ? Mma16816<__half>::pack(sum.x, sum.y) : Mma16816<__nv_bfloat16>::pack(sum.x, sum.y);
+        w.y = p.out_f16 ? Mma16816<__half>::pack(sum.z, sum.w) : Mma16816<__nv_bfloat16>::pack(sum.z, sum.w);
+        *reinterpret_cast<uint2*>(dst) = w;
+      } else {
+        const float v[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (n0 + j < p.n) {
+            if (p.out_f16)
+              reinterpret_cast<__half*>(dst)[j] = __float2half_rn(v[j]);
+            else
+              reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(v[j]);
+          }
+        }
+      }
+    }
+  }
+}
+
 __global__ void __launch_bounds__(kWideThreads, 1)
     fp8_gemm_wide_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                          const GemmParams p) {
@@ -787,66 +841,11 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         }
         if (epi_tid == 0) wide_stamp(p, 3);
         cluster_sync_all();
-        // This CTA adds the 4-column groups [g_lo, g_hi) of the tile's 64 over all ranks, in rank order.
-        const int g_lo = 64 * rank / split, g_hi = 64 * (rank + 1) / split, groups = g_hi - g_lo;
-        const uint32_t park_addr = smem_u32(stage_base);
-        const bool vec = (p.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 7) == 0);
-        // Two (row, group) items per thread at a time, every peer's load of both in flight together.
-        for (int i0 = epi_tid; i0 < kTileR * groups; i0 += 2 * kEpiThreads) {
-          float4 part[2][4];
-          uint32_t slot[2];
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int i = i0 + u * kEpiThreads;
-            const int row = i / groups, g = g_lo + i % groups;
-            slot[u] = park_addr + (uint32_t)((row * 64 + (g ^ (row & 7))) * 16);
-          }
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            if (i0 + u * kEpiThreads < kTileR * groups) {
-#pragma unroll
-              for (int peer = 0; peer < 4; ++peer)
-                if (peer < split) part[u][peer] = ld_cluster_f4(slot[u], (uint32_t)peer);
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < 2; ++u) {
-            const int i = i0 + u * kEpiThreads;
-            if (i >= kTileR * groups) continue;
-            const int row = i / groups, g = g_lo + i % groups;
-            float4 sum = part[u][0];
-#pragma unroll
-            for (int peer = 1; peer < 4; ++peer) {
-              if (peer < split) {
-                sum.x += part[u][peer].x;
-                sum.y += part[u][peer].y;
-                sum.z += part[u][peer].z;
-                sum.w += part[u][peer].w;
-              }
-            }
-            const int tok = tok0 + row, n0 = it.tn * BN + g * 4;
-            if (tok < p.m && n0 < p.n) {
-              uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + (long long)tok * p.ldy + n0;
-              if (vec && n0 + 4 <= p.n) {
-                uint2 w;
-                w.x = p.out_f16 ? Mma16816<__half>::pack(sum.x, sum.y) : Mma16816<__nv_bfloat16>::pack(sum.x, sum.y);
-                w.y = p.out_f16 ? Mma16816<__half>::pack(sum.z, sum.w) : Mma16816<__nv_bfloat16>::pack(sum.z, sum.w);
-                *reinterpret_cast<uint2*>(dst) = w;
-              } else {
-                const float v[4] = {sum.x, sum.y, sum.z, sum.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  if (n0 + j < p.n) {
-                    if (p.out_f16)
-                      reinterpret_cast<__half*>(dst)[j] = __float2half_rn(v[j]);
-                    else
-                      reinterpret_cast<__nv_bfloat16*>(dst)[j] = __float2bfloat16_rn(v[j]);
-                  }
-                }
-              }
-            }
-          }
-        }
+        if (epi_tid == 0) wide_stamp(p, 8);
+        if (split == 2)
+          wide_cluster_reduce<2>(p, smem_u32(stage_base), rank, epi_tid, tok0, it.tn * BN);
+        else
+          wide_cluster_reduce<4>(p, smem_u32(stage_base), rank, epi_tid, tok0, it.tn * BN);
         if (epi_tid == 0) wide_stamp(p, 4);
         cluster_sync_all();  // no CTA leaves while a peer may still read its partial
       }
