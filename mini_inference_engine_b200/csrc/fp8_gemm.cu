@@ -24,6 +24,7 @@
 //   * Every mbarrier wait is bounded; a wait that runs out sets
 //     MIE_STATUS_WAIT_TIMEOUT, the roles fall through to the common exit and
 //     TMEM is released.
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 
@@ -57,6 +58,7 @@ struct GemmParams {
   int out_f16;
   int* status;
   long long* trace;       // optional [CTAs][16] globaltimer stamps (profiling aid), or null
+  int prefetch;           // weights of the first K blocks are requested before the launch-chain wait
 };
 
 __device__ __forceinline__ void trace_stamp(const GemmParams& p, int slot) {
@@ -171,6 +173,17 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // Barriers, tensor-map prefetch and the TMEM allocation above overlap the tail of the previous kernel.
+  // So can the weights (nothing on the stream writes them): the producer requests the weight half of its
+  // first stages before the launch-chain wait and adds the activation half afterwards.
+  uint32_t prefetched = 0;
+  if (kSwap && p.prefetch && warp == E && lane == 0) {
+    const uint64_t stream_policy = l2_evict_first_policy();
+    for (int kb = kb_first; kb < kb_last && prefetched < (uint32_t)kStages; ++kb, ++prefetched) {
+      mbar_expect_tx(&full_bar[prefetched], S::kStageBytes);
+      tma_load_2d_hint(stage_base + (size_t)prefetched * S::kStageBytes, &map_r, &full_bar[prefetched], kb * kBlockK,
+                       tr * kTileR, stream_policy);
+    }
+  }
   chain_wait();
   chain_release();
   if (threadIdx.x == 0) {
@@ -192,11 +205,15 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
       uint32_t n = 0;
       for (int kb = kb_first; kb < kb_last; ++kb, ++n) {
         const int s = n % kStages;
+        uint8_t* dst = stage_base + (size_t)s * S::kStageBytes;
+        if (n < prefetched) {  // the weight half is already on its way
+          tma_load_2d(dst + kTileR * kBlockK, &map_c, &full_bar[s], kb * kBlockK, tc * BN);
+          continue;
+        }
         if (!mbar_wait_bounded(&empty_bar[s], ((n / kStages) & 1u) ^ 1u)) {
           raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
           break;
         }
-        uint8_t* dst = stage_base + (size_t)s * S::kStageBytes;
         mbar_expect_tx(&full_bar[s], S::kStageBytes);
         if (kSwap)  // decode-time weights are streamed once: keep them from flushing L2
           tma_load_2d_hint(dst, &map_r, &full_bar[s], kb * kBlockK, tr * kTileR, stream_policy);
@@ -647,6 +664,19 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // Barriers, tensor-map prefetch and the TMEM allocation above overlap the tail of the previous kernel.
+  // So can the weights (nothing on the stream writes them): the producer requests the weight half of its
+  // first stages before the launch-chain wait and adds the activation half afterwards.
+  uint32_t prefetched = 0;
+  if (p.prefetch && warp == E && lane == 0) {
+    WideItem first;
+    if (wide_item(tiles, tiles_m, kb_total, split, rank, 0, first)) {
+      for (int kb = first.k0; kb < first.k1 && prefetched < (uint32_t)kStages; ++kb, ++prefetched) {
+        mbar_expect_tx(&full_bar[prefetched], kWideStageBytes);
+        tma_load_2d(stage_base + (size_t)prefetched * kWideStageBytes + kTileR * kBlockK, &map_w,
+                    &full_bar[prefetched], kb * kBlockK, first.tn * BN);
+      }
+    }
+  }
   chain_wait();
   chain_release();
   if (threadIdx.x == 0) wide_stamp(p, 0);
@@ -668,12 +698,16 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       for (int idx = 0; ok && wide_item(tiles, tiles_m, kb_total, split, rank, idx, it); ++idx) {
         for (int kb = it.k0; kb < it.k1; ++kb, ++n) {
           const int s = n % kStages;
+          uint8_t* dst = stage_base + (size_t)s * kWideStageBytes;
+          if (n < prefetched) {  // the weight half is already on its way
+            tma_load_2d(dst, &map_x, &full_bar[s], kb * kBlockK, it.tm * kTileR);
+            continue;
+          }
           if (!mbar_wait_bounded(&empty_bar[s], ((n / kStages) & 1u) ^ 1u)) {
             raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
             ok = false;
             break;
           }
-          uint8_t* dst = stage_base + (size_t)s * kWideStageBytes;
           mbar_expect_tx(&full_bar[s], kWideStageBytes);
           tma_load_2d(dst, &map_x, &full_bar[s], kb * kBlockK, it.tm * kTileR);
           tma_load_2d(dst + kTileR * kBlockK, &map_w, &full_bar[s], kb * kBlockK, it.tn * BN);
@@ -1145,6 +1179,11 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
   p.out_f16 = out_dtype == MIE_DTYPE_F16;
   p.status = status;
   p.trace = reinterpret_cast<long long*>(trace);
+  static const int prefetch = [] {
+    const char* v = getenv("MIE_GEMM_PREFETCH");
+    return v != nullptr && v[0] == '0' ? 0 : 1;  // MIE_GEMM_PREFETCH=0 turns it off
+  }();
+  p.prefetch = prefetch;
 
   CUtensorMap mr, mc;
   if (swap) {
