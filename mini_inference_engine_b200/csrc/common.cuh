@@ -45,6 +45,9 @@ int cuda_fail(cudaError_t err, const char* what);
 int sm_count();
 void count_launch();  // every kernel launch of this library bumps a host-side counter
 bool chained_launch_enabled();  // false when MIE_PDL=0
+// Once per kernel and device: ask for the largest shared-memory carve-out, so that a small kernel and the
+// GEMM / attention kernel chained after it (200 KB of shared memory) can be resident on one SM together.
+void prefer_shared_carveout(const void* kernel);
 
 #ifdef __CUDACC__
 // Programmatic dependent launch.  A kernel launched with launch_chained() may be scheduled while the kernel
@@ -68,6 +71,7 @@ inline cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 blo
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attr;
   config.numAttrs = chained_launch_enabled() ? 1 : 0;
+  prefer_shared_carveout(reinterpret_cast<const void*>(kernel));
   return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 #endif

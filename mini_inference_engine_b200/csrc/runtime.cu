@@ -5,6 +5,8 @@
 
 #include <atomic>
 #include <mutex>
+#include <set>
+#include <utility>
 
 #include "common.cuh"
 
@@ -33,6 +35,24 @@ bool chained_launch_enabled() {
     return !(v != nullptr && v[0] == '0');
   }();
   return enabled;
+}
+
+void prefer_shared_carveout(const void* kernel) {
+  static const bool enabled = [] {
+    const char* v = getenv("MIE_CARVEOUT");
+    return !(v != nullptr && v[0] == '0');  // MIE_CARVEOUT=0 turns the hint off
+  }();
+  if (!enabled) return;
+  static std::mutex mu;
+  static std::set<std::pair<const void*, int>> done;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  std::lock_guard<std::mutex> lock(mu);
+  if (done.insert({kernel, dev}).second) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=
+        cudaSuccess)
+      (void)cudaGetLastError();
+  }
 }
 
 int sm_count() {

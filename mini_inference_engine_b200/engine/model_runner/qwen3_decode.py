@@ -456,15 +456,22 @@ class Qwen3DecodeRunner:
             buffers.input_ids.copy_(next_ids)
             buffers.block_tables.copy_(tables_dev)
             buffers.sequence_lengths.copy_(current + 1)
-        for _ in range(max_new_tokens - 1):
-            if buffers is not None:
+        if buffers is not None:
+            # The graph feeds its own tokens back, so the steps are queued back to back; every step's tokens
+            # are kept on the device and read in one copy at the end (no host round trip between steps).
+            history = torch.empty(max_new_tokens - 1, batch, dtype=torch.int64, device=device)
+            for step in range(max_new_tokens - 1):
                 self.replay(batch)
-                next_ids = buffers.output_tokens.clone()
-            else:
+                history[step].copy_(buffers.output_tokens)
+            for step_tokens in history.tolist():
+                for row, token in enumerate(step_tokens):
+                    outputs[row].append(int(token))
+        else:
+            for _ in range(max_new_tokens - 1):
                 current = current + 1
                 next_ids = self.decode_forward(next_ids, current, tables_dev)
-            for row, token in enumerate(next_ids.tolist()):
-                outputs[row].append(int(token))
+                for row, token in enumerate(next_ids.tolist()):
+                    outputs[row].append(int(token))
         self.check_status()
         return outputs
 
