@@ -200,7 +200,7 @@ def run_reference_arm(args: argparse.Namespace) -> None:
         "e2e": {"value": base["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "wall_seconds": time.perf_counter() - started,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -229,7 +229,7 @@ def run_config3(args, shape, device, rank, world, group) -> None:
     torch.cuda.synchronize(device)
     wall = time.perf_counter() - t0
     if rank == 0:
-        print(json.dumps({
+        emit({
             "metric": "output tok/s, 8 requests x 2048-token prompts, 128 new tokens (configuration 3)",
             "value": requests * new_tokens / wall, "unit": "tok/s", "n_gpus": world, "seconds": wall,
             "vs_baseline": requests * new_tokens / wall / 160.6,  # the reference's published L4 number
@@ -237,14 +237,31 @@ def run_config3(args, shape, device, rank, world, group) -> None:
             "config": {"workload": "config3", "requests": requests, "prompt_tokens": prompt_len,
                        "new_tokens": new_tokens, "includes": "packed prefill + 127 graph decode steps (the graph was captured by the warm-up generation)"},
             "tokens_first_request": outputs[0][:8],
-        }), flush=True)
+        })
     if world > 1:
         torch.distributed.barrier()
         sys.stdout.flush()
         os._exit(0)
 
 
+_RESULT_OUT = None
+
+
+def emit(line: dict) -> None:
+    """Print the one JSON line on the process's original stdout."""
+
+    out = _RESULT_OUT if _RESULT_OUT is not None else sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def main() -> None:
+    # Libraries (NCCL with NCCL_DEBUG set, for one) write banners to file descriptor 1; the contract is ONE
+    # JSON line on stdout, so everything else that goes to fd 1 is sent to stderr.
+    global _RESULT_OUT
+    sys.stdout.flush()
+    _RESULT_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     args = parse_args()
     if args.watchdog > 0:
         import faulthandler
@@ -450,7 +467,7 @@ def main() -> None:
         }
         if args.layers is not None:
             line["invalid"] = "debug run with fewer layers"
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         # Captured graphs still hold NCCL kernels; tearing the communicator down under them can block, so
         # leave together and let process exit reclaim everything.
