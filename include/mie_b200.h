@@ -263,6 +263,9 @@ int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t
  * (1 = never split), 0 lets the library choose.  trace is a profiling aid:
  * NULL, or a device buffer of 16 int64 per CTA that receives %globaltimer
  * stamps of the kernel's phases.  Uses no global scratch memory.
+ * The weight tiles of the first pipeline stages are requested while the kernel
+ * queued before this one may still be running (programmatic dependent launch):
+ * w8 must not be written by that kernel (MIE_GEMM_PREFETCH=0 lifts this).
  */
 int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
                  int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy, int32_t out_dtype,

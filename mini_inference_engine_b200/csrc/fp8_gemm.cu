@@ -1010,13 +1010,15 @@ int operand_map(const void* ptr, long long rows, long long k, long long ld, int 
 
 // K-split factor for a shape with `tiles` output tiles of `kb_total` K blocks.  Cost model in units of
 // one K block of a 256-column tile: waves * (K blocks per CTA + fixed cost) + the cluster reduction
-// (which grows with the tile width).  Only cluster sizes 1, 2 and 4 are used: 3 and 8 co-schedule badly
-// with one 200 KB CTA per SM (measured), and larger splits leave too little work per CTA.
+// (which grows with the tile width).  Cluster sizes 1, 2 and 4 are used, and 8 for the narrow tiles that
+// run two 100 KB CTAs per SM (o / down at up to 32 tokens: 160 CTAs instead of 80); 3 and 8 co-schedule
+// badly with one 200 KB CTA per SM (measured), and larger splits leave too little work per CTA.
 int choose_split(long long tiles, int kb_total, int bn, int ctas_per_sm, int max_split) {
   const int slots = sm_count() * ctas_per_sm;
   int best = 1;
   double best_cost = 1e30;
-  for (int s = 1; s <= 4; s *= 2) {
+  const int limit = ctas_per_sm == 2 ? 8 : 4;
+  for (int s = 1; s <= limit; s *= 2) {
     if (s > kb_total || (max_split > 0 && s > max_split)) break;
     const long long ctas = tiles * s;
     const double waves = (double)((ctas + slots - 1) / slots);
