@@ -333,6 +333,29 @@ int mie_qkv_norm_rope_write(const void* qkv, int64_t ld, const void* q_weight, c
                             int32_t kv_heads, int32_t block_size, int32_t num_blocks, int32_t table_rows,
                             int32_t table_width, float eps, int32_t* status, void* stream);
 
+/* ------------------------------------------------------------------------
+ * lm_head + greedy sampling
+ * ---------------------------------------------------------------------- */
+
+/*
+ * Replaces the last two operations of the decode step, logits = hidden @
+ * lm_head^T in bf16 followed by argmax (engine/model_runner/qwen3_mixed.py:
+ * 164-174, engine/serving/chunked_prefill.py:224-229), without writing the
+ * [batch, vocab] logits: tokens[b] = the lowest vocabulary index whose bf16
+ * logit is the largest of row b.  x [batch, k] bf16 (row stride ldx elements),
+ * w [vocab, k] bf16 (row stride ldw elements; a slice of a larger table for a
+ * vocabulary-sharded head, whose first row has global index vocab_offset),
+ * batch <= 256.  keys: batch uint64 words of device memory owned by the
+ * caller that are ZERO on entry; the call leaves them zero again (allocate and
+ * clear them once).  tokens: int64 [batch], global indices.  values: NULL, or
+ * int32 [batch] receiving an order-preserving key of each winning bf16 logit
+ * (what ranks of a sharded head compare).  Base pointers and row strides must
+ * be multiples of 16 bytes.  Two launches on the given stream.
+ */
+int mie_lm_head_argmax(const void* x, int64_t ldx, const void* w, int64_t ldw, int32_t batch, int32_t vocab,
+                       int32_t k, int64_t vocab_offset, uint64_t* keys, int64_t* tokens, int32_t* values,
+                       int32_t* status, void* stream);
+
 /* ---------------------------------------------------------------------------
  * Tensor-parallel exchange (no counterpart in the reference, which runs on one
  * GPU; these serve the head-sharded TP = 2/4/8 decode step).

@@ -103,6 +103,8 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "mie_qkv_norm_rope_write": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, IndexT,
                                                IndexT, IndexT, c_void_p, View4T, View4T, c_int32, c_int32, c_int32,
                                                c_int32, c_int32, c_int32, c_int32, c_float, c_void_p, c_void_p]),
+    "mie_lm_head_argmax": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int32, c_int32, c_int32, c_int64,
+                                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "mie_ipc_export": (ctypes.c_int, [c_void_p, c_void_p, ctypes.POINTER(c_int64)]),
     "mie_ipc_open": (ctypes.c_int, [c_void_p, c_int64, ctypes.POINTER(c_void_p)]),
     "mie_ipc_close": (ctypes.c_int, [c_void_p, c_int64]),

@@ -236,6 +236,10 @@ class Qwen3DecodeRunner:
                                       max_batch * max_context, self.device)
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, DecodeBuffers]] = {}
         self.launches_per_step = 0
+        # lm_head + greedy sampling: one pass over the tied embedding that never writes the logits
+        # (mie_lm_head_argmax) unless MIE_LM_HEAD=cublas; its per-row keys are zero between calls.
+        self.fused_lm_head = os.environ.get("MIE_LM_HEAD", "fused") != "cublas"
+        self._lm_keys = torch.zeros(256, dtype=torch.int64, device=self.device)
         # Tensor parallel decode: the all-reduce after o_proj / down_proj is fused into the residual add +
         # RMSNorm + quantisation kernel over peer memory unless MIE_TP_EXCHANGE=nccl (or fused_exchange=False).
         if fused_exchange is None:
@@ -355,12 +359,32 @@ class Qwen3DecodeRunner:
             next_norm = self.weights.final_norm if last else layers[index + 1].input_norm
             final, residual, quantized = self._row_parallel_then_norm(act_q, layer.down, layer.down_scale, batch, inter,
                                                                       residual, next_norm, quantize=not last)
+        if self.fused_lm_head and self.tp == 1 and not return_logits and batch <= 256:
+            tokens = self.greedy_tokens(final)
+            self.launches_per_step = int(lib.mie_launch_count() - launches_before)
+            return tokens
         logits = torch.matmul(final, self.weights.lm_head.t())
         self.launches_per_step = int(lib.mie_launch_count() - launches_before)
         if self.tp == 1:
             tokens = logits.argmax(dim=-1)
             return (tokens, logits) if return_logits else tokens
         return sharded_greedy_tokens(logits, self.weights.vocab_start, self.tp, self.group)
+
+    def greedy_tokens(self, final: torch.Tensor) -> torch.Tensor:
+        """Greedy next tokens of normed hidden rows ``[rows, hidden]`` (rows <= 256): the bf16 product with the
+        tied lm_head and its argmax in one pass (reference: engine/model_runner/qwen3_mixed.py:164-174)."""
+
+        lib = _lib.load()
+        rows = int(final.shape[0])
+        if final.stride(1) != 1 or final.stride(0) % 8 != 0 or final.data_ptr() % 16 != 0:
+            final = final.contiguous()
+        head = self.weights.lm_head
+        tokens = torch.empty(rows, dtype=torch.int64, device=self.device)
+        _lib.check(lib.mie_lm_head_argmax(_lib.ptr(final), final.stride(0), _lib.ptr(head), head.stride(0), rows,
+                                          head.shape[0], head.shape[1], self.weights.vocab_start,
+                                          _lib.ptr(self._lm_keys), _lib.ptr(tokens), None, _lib.ptr(self.status),
+                                          _lib.stream_arg(self.device)))
+        return tokens
 
     # -- packed prefill (whole prompts or chunks over a cached prefix) ----------------------------------
 

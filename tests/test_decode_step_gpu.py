@@ -94,8 +94,9 @@ def test_launch_count_is_reported(device):
     runner.decode_forward(torch.tensor([1], device=device), torch.tensor([3], dtype=torch.int32, device=device),
                           tables)
     # Per layer: add+RMSNorm(+quant) x2, SiLU*up(+quant), 4 GEMMs, q/k-norm + RoPE + KV write, decode attention
-    # and its merge (o_proj quantisation fused into both); once per step: the split-KV plan and the final norm.
-    assert runner.launches_per_step == 2 * 10 + 2
+    # and its merge (o_proj quantisation fused into both); once per step: the split-KV plan, the final norm and
+    # the two launches of the fused lm_head + greedy sampling.
+    assert runner.launches_per_step == 2 * 10 + 2 + 2
 
 
 def _check_tokens(got, expected, logits_ref, where):
