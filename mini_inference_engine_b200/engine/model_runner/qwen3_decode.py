@@ -206,6 +206,22 @@ def sharded_greedy_tokens(local_logits: torch.Tensor, vocab_start: int, tp_size:
     return gathered[winner, torch.arange(batch, device=local_logits.device), 1].long()
 
 
+def sharded_greedy_from_pairs(tokens: torch.Tensor, values: torch.Tensor, tp_size: int, group=None) -> torch.Tensor:
+    """Global greedy tokens from every rank's local winner: ``tokens`` are global vocabulary indices, ``values``
+    order-preserving keys of the winning bf16 logits (``mie_lm_head_argmax``).  The largest value wins; among
+    equal values the lowest rank, whose shard holds the lower indices."""
+
+    if tp_size == 1:
+        return tokens
+    rows = tokens.shape[0]
+    pair = torch.stack((values.long(), tokens), dim=-1).contiguous()
+    flat = torch.empty(tp_size * rows, 2, dtype=torch.int64, device=tokens.device)
+    torch.distributed.all_gather_into_tensor(flat, pair, group=group)
+    gathered = flat.view(tp_size, rows, 2)
+    winner = gathered[:, :, 0].argmax(dim=0)
+    return gathered[winner, torch.arange(rows, device=tokens.device), 1]
+
+
 class Qwen3DecodeRunner:
     """Decode steps of a Qwen3-shaped FP8 model over paged KV, eager or as a CUDA graph."""
 
@@ -359,7 +375,7 @@ class Qwen3DecodeRunner:
             next_norm = self.weights.final_norm if last else layers[index + 1].input_norm
             final, residual, quantized = self._row_parallel_then_norm(act_q, layer.down, layer.down_scale, batch, inter,
                                                                       residual, next_norm, quantize=not last)
-        if self.fused_lm_head and self.tp == 1 and not return_logits and batch <= 256:
+        if self.fused_lm_head and not return_logits and batch <= 256:
             tokens = self.greedy_tokens(final)
             self.launches_per_step = int(lib.mie_launch_count() - launches_before)
             return tokens
@@ -380,11 +396,12 @@ class Qwen3DecodeRunner:
             final = final.contiguous()
         head = self.weights.lm_head
         tokens = torch.empty(rows, dtype=torch.int64, device=self.device)
+        values = torch.empty(rows, dtype=torch.int32, device=self.device) if self.tp > 1 else None
         _lib.check(lib.mie_lm_head_argmax(_lib.ptr(final), final.stride(0), _lib.ptr(head), head.stride(0), rows,
                                           head.shape[0], head.shape[1], self.weights.vocab_start,
-                                          _lib.ptr(self._lm_keys), _lib.ptr(tokens), None, _lib.ptr(self.status),
-                                          _lib.stream_arg(self.device)))
-        return tokens
+                                          _lib.ptr(self._lm_keys), _lib.ptr(tokens), _lib.ptr(values),
+                                          _lib.ptr(self.status), _lib.stream_arg(self.device)))
+        return sharded_greedy_from_pairs(tokens, values, self.tp, self.group) if self.tp > 1 else tokens
 
     # -- packed prefill (whole prompts or chunks over a cached prefix) ----------------------------------
 
@@ -435,6 +452,8 @@ class Qwen3DecodeRunner:
         last_rows = (cu_seqlens[1:].long() - 1).clamp_min(0)
         final, _, _ = self._norm(mlp_out.index_select(0, last_rows), self.weights.final_norm,
                                  residual.index_select(0, last_rows), quantize=False)
+        if self.fused_lm_head and not return_logits and final.shape[0] <= 256:
+            return self.greedy_tokens(final)
         logits = torch.matmul(final, self.weights.lm_head.t())
         picked = sharded_greedy_tokens(logits, self.weights.vocab_start, self.tp, self.group)
         return (picked, logits) if return_logits else picked
@@ -543,4 +562,4 @@ class Qwen3DecodeRunner:
 
 
 __all__ = ["DecodeBuffers", "LayerWeights", "Qwen3DecodeRunner", "Qwen3Shape", "Qwen3Weights",
-           "quantize_weight_blocks", "rope_table", "sharded_greedy_tokens"]
+           "quantize_weight_blocks", "rope_table", "sharded_greedy_from_pairs", "sharded_greedy_tokens"]

@@ -19,6 +19,7 @@ from mini_inference_engine_b200 import workloads
 from mini_inference_engine_b200.engine.model_runner.qwen3_decode import (
     Qwen3Shape,
     Qwen3Weights,
+    sharded_greedy_from_pairs,
     sharded_greedy_tokens,
 )
 from oracle import qwen3_model
@@ -64,8 +65,19 @@ def _worker(rank: int, world: int, port: int, queue) -> None:
             dist.all_reduce(summed)
             return summed.to(tensor.dtype)
 
-        tokens = _step(weights, world, pools, ids, lengths, tables, all_reduce=all_reduce,
-                       pick_tokens=lambda logits: sharded_greedy_tokens(logits, weights.vocab_start, world))
+        seen = {}
+
+        def pick(logits):
+            # The fused lm_head reports (global index, order key of the bf16 logit) per row; its exchange must
+            # choose the same tokens as the exchange of the logits themselves.
+            best = logits.to(torch.bfloat16).float().max(dim=-1)
+            bits = best.values.to(torch.bfloat16).view(torch.int16).int() & 0xFFFF
+            keys = torch.where((bits & 0x8000) != 0, ~bits & 0xFFFF, bits | 0x8000).to(torch.int32)
+            seen["pairs"] = sharded_greedy_from_pairs(best.indices + weights.vocab_start, keys, world)
+            return sharded_greedy_tokens(logits, weights.vocab_start, world)
+
+        tokens = _step(weights, world, pools, ids, lengths, tables, all_reduce=all_reduce, pick_tokens=pick)
+        assert torch.equal(seen["pairs"], tokens)
         queue.put((rank, tokens.tolist()))
     finally:
         dist.destroy_process_group()
