@@ -3,6 +3,7 @@
     python -m mini_inference_engine_b200.microbench decode --concurrency 64
     python -m mini_inference_engine_b200.microbench gemm --shape qkv --rows 256
     python -m mini_inference_engine_b200.microbench prefill --requests 6
+    python -m mini_inference_engine_b200.microbench lm_head --rows 8
 
 Each prints one JSON line with the CUDA-event time per launch (median of the repeats, L2 flushed by a
 256 MiB fill between repeats) and the algorithmic bytes / FLOPs of the launch.
@@ -16,7 +17,7 @@ import statistics
 
 import torch
 
-from . import workloads
+from . import _lib, workloads
 from .engine.kernels import sm89_fp8
 from .engine.kv_cache import triton_flash_prefill_attention, triton_write_packed_kv
 from .engine.kv_cache.triton_paged_attention import decode_scratch, launch_decode_attention
@@ -105,6 +106,26 @@ def prefill(args, device) -> dict:
             "us_per_launch": ms * 1e3, "tflops": flops / ms / 1e9}
 
 
+def lm_head(args, device) -> dict:
+    vocab, hidden = 151936, 2560
+    weight = (torch.randn(vocab, hidden, device=device) * 0.02).to(torch.bfloat16)
+    x = torch.randn(args.rows, hidden, device=device).to(torch.bfloat16)
+    keys = torch.zeros(256, dtype=torch.int64, device=device)
+    tokens = torch.empty(args.rows, dtype=torch.int64, device=device)
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    lib = _lib.load()
+
+    def run():
+        _lib.check(lib.mie_lm_head_argmax(_lib.ptr(x), x.stride(0), _lib.ptr(weight), weight.stride(0), args.rows,
+                                          vocab, hidden, 0, _lib.ptr(keys), _lib.ptr(tokens), None, _lib.ptr(status),
+                                          _lib.stream_arg(device)))
+
+    ms = _time(run, args.repeats, device)
+    algorithmic = vocab * hidden * 2 + args.rows * hidden * 2 + args.rows * 8
+    return {"kernel": "lm_head + greedy sampling", "rows": args.rows, "us_per_launch": ms * 1e3,
+            "algorithmic_bytes": algorithmic, "gb_per_s": algorithmic / ms / 1e6}
+
+
 def main() -> None:
     parser = argparse.ArgumentParser(description=__doc__)
     sub = parser.add_subparsers(dest="command", required=True)
@@ -118,11 +139,13 @@ def main() -> None:
     p.add_argument("--copies", type=int, default=4)
     p = sub.add_parser("prefill")
     p.add_argument("--requests", type=int, default=6)
-    for name in ("decode", "gemm", "prefill"):
+    p = sub.add_parser("lm_head")
+    p.add_argument("--rows", type=int, default=8)
+    for name in ("decode", "gemm", "prefill", "lm_head"):
         sub.choices[name].add_argument("--repeats", type=int, default=9)
     args = parser.parse_args()
     device = torch.device("cuda", 0)
-    result = {"decode": decode, "gemm": gemm, "prefill": prefill}[args.command](args, device)
+    result = {"decode": decode, "gemm": gemm, "prefill": prefill, "lm_head": lm_head}[args.command](args, device)
     print(json.dumps(result))
 
 
