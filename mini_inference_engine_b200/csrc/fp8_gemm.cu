@@ -118,6 +118,10 @@ template <int BN, int E, bool kSwap>
 __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
     fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_c,
                     const GemmParams p) {
+  // Only the swapped orientation with four promotion warps is instantiated (up to 128 tokens); the token-major
+  // orientation of this template is kept as the reference form of the arithmetic, the product path for more
+  // tokens is fp8_gemm_wide_kernel.
+  static_assert(kSwap && E == 4, "more than 128 tokens run fp8_gemm_wide_kernel");
   using S = GemmSmem<BN, E, kSwap>;
   using SS = ScaleStage<BN, kSwap>;
   constexpr int kStages = S::kStages;
