@@ -1161,7 +1161,10 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
   MIE_CHECK_ARG(ldy >= n && a_scale_ld >= m && w_scale_ld >= (k + 127) / 128, "invalid leading dimension");
   if (m == 0) return MIE_OK;
 
-  const bool swap = m <= 128;
+  // Up to 128 tokens stream the weights through the swapped kernel, unless that needs a second wave of
+  // full-K tiles (more 128-row weight tiles than SMs at more than 32 tokens, where only one of its CTAs
+  // fits an SM: gate_up): the wide kernel's 256-row tiles then finish in one round.
+  const bool swap = m <= 128 && !(m > 32 && (n + kTileR - 1) / kTileR > sm_count());
   const int bn = swap ? swap_bn(m) : 256;
   const int kb = (k + kBlockK - 1) / kBlockK;
   const long long tiles_r = swap ? (n + kTileR - 1) / kTileR : (m + kTileR - 1) / kTileR;
