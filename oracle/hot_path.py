@@ -19,7 +19,7 @@ exists only inside Triton kernels, engine/kernels/sm89_fp8.py:220-398, and the
 fallback ``transformers.integrations.finegrained_fp8.fp8_linear`` of the pinned
 transformers 5.14.1 is GPU-only and absent from the installed 5.5.0), so
 ``fp8_linear`` below restates those kernels' arithmetic and is pinned only
-against the double-precision dequantised product the reference's judge uses
+against the double-precision dequantised product the reference's kernel benchmark checks against
 (benchmarks/commands/run_kernel_track.py:210-217): parity unpinned for the
 bit pattern of the FP8 product, pinned for the 1e-2 tolerance.
 """

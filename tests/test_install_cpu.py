@@ -9,7 +9,8 @@ from pathlib import Path
 
 import pytest
 
-REFERENCE = Path(os.environ.get("MIE_REFERENCE_CHECKOUT", "/root/reference"))
+# A checkout of the reference: MIE_REFERENCE_CHECKOUT, else a directory named "reference" beside this repository.
+REFERENCE = Path(os.environ.get("MIE_REFERENCE_CHECKOUT", str(Path(__file__).resolve().parents[2] / "reference")))
 
 
 @pytest.mark.skipif(not (REFERENCE / "engine" / "kv_cache").is_dir(), reason="no reference checkout on this host")
