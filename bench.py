@@ -179,6 +179,17 @@ def cpu_decode_baseline(sample_sequences: int = 4, max_context: int = 4096, repe
     }
 
 
+def use_all_host_cores() -> int:
+    """Let torch's CPU kernels use every core this process may run on; returns the thread count."""
+
+    try:
+        cores = len(os.sched_getaffinity(0))
+    except AttributeError:
+        cores = os.cpu_count() or 1
+    torch.set_num_threads(max(cores, 1))
+    return torch.get_num_threads()
+
+
 def run_reference_arm(args: argparse.Namespace) -> None:
     """The reference's own CPU path for this metric: its torch block-wise attention and the FP8 linear
     restated on the CPU (the reference has no CPU FP8 kernel), on all host threads."""
@@ -186,6 +197,9 @@ def run_reference_arm(args: argparse.Namespace) -> None:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # A multi-process launcher exports OMP_NUM_THREADS=1 to its workers; the baseline uses every host core
+    # at every N so that all runs share one denominator.
+    use_all_host_cores()
     repeats = max(1, min(args.steps, 2))
     started = time.perf_counter()
     base = cpu_decode_baseline(repeats=repeats)
@@ -239,9 +253,24 @@ def run_config3(args, shape, device, rank, world, group) -> None:
             "tokens_first_request": outputs[0][:8],
         })
     if world > 1:
-        torch.distributed.barrier()
-        sys.stdout.flush()
-        os._exit(0)
+        leave_together(runner, device)
+
+
+def leave_together(runner, device) -> None:
+    """End a multi-rank run: drop the captured graphs (they hold NCCL kernels and peer-memory pointers), wait
+    for the device and for every rank, unmap the peers' exchange blocks, then exit without running the
+    communicator's destructor (destroying a communicator that graphs had captured blocked one earlier run;
+    with the graphs gone and NVLS off nothing is bound to a peer when the process exits)."""
+
+    runner._graphs.clear()
+    torch.cuda.synchronize(device)
+    torch.distributed.barrier()
+    torch.cuda.synchronize(device)
+    if runner.exchange is not None:
+        runner.exchange.close()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 _RESULT_OUT = None
@@ -286,6 +315,9 @@ def main() -> None:
     device = torch.device("cuda", local_rank)
     group = None
     if world > 1:
+        # No NVLink multicast (NVLS) objects: a rank that leaves while its memory is bound to one can raise
+        # NVLink faults on its peers, and the exchange kernels of this library use plain peer loads anyway.
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         torch.distributed.init_process_group("nccl", device_id=device)
         group = torch.distributed.group.WORLD
     tp = world
@@ -433,8 +465,20 @@ def main() -> None:
                 "algorithmic_bytes_per_launch": algorithmic, "ms_per_launch": attn_ms}
     runner.check_status()
 
+    # Every rank holds the tokens of the last replayed step; under tensor parallelism they must be identical.
+    tokens_agree = None
+    if world > 1:
+        mine = [buffers.output_tokens.clone()]
+        if e2e is not None:
+            mine.append(host_ids.to(device))
+        mine = torch.cat(mine)
+        gathered = torch.empty(world, mine.numel(), dtype=torch.int64, device=device)
+        torch.distributed.all_gather_into_tensor(gathered, mine)
+        tokens_agree = bool((gathered == gathered[0:1]).all().item())
+
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+    if rank == 0 and not args.no_cpu_baseline:
+        use_all_host_cores()
         try:
             cpu_all = cpu_decode_baseline(layer_source=weights.layers[0], embedding=weights.embedding,
                                           final_norm=weights.final_norm)
@@ -461,7 +505,7 @@ def main() -> None:
                                 if runner.exchange is not None else "nccl all-reduce"),
             },
             "roofline": roofline, "cpu_baseline": cpu, "e2e": e2e,
-            "gpu_launches": launches_per_step * steps, "clocks": clocks,
+            "gpu_launches": launches_per_step * steps, "clocks": clocks, "tp_tokens_agree": tokens_agree,
             "step_hbm_bytes_per_gpu": step_bytes,
             "step_hbm_frac_of_peak": step_bytes / (elapsed_ms / steps / 1e3) / 1e9 / peak,
         }
@@ -469,12 +513,7 @@ def main() -> None:
             line["invalid"] = "debug run with fewer layers"
         emit(line)
     if world > 1:
-        # Captured graphs still hold NCCL kernels; tearing the communicator down under them can block, so
-        # leave together and let process exit reclaim everything.
-        torch.distributed.barrier()
-        torch.cuda.synchronize(device)
-        sys.stdout.flush()
-        os._exit(0)
+        leave_together(runner, device)
 
 
 if __name__ == "__main__":

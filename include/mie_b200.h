@@ -43,6 +43,7 @@ extern "C" {
 #define MIE_STATUS_WAIT_TIMEOUT 16   /* a bounded device-side wait gave up */
 #define MIE_STATUS_MAX_LENGTH 32     /* attention read length beyond max_sequence_length */
 #define MIE_STATUS_CAPACITY 64       /* work plan did not fit the scratch the caller sized */
+#define MIE_STATUS_NO_TOKEN 128      /* greedy sampling saw no candidate for a row; token 0 was written */
 
 /* Element types of K/V pages, queries and activations. */
 #define MIE_DTYPE_BF16 0
@@ -251,25 +252,36 @@ int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t
  * Replaces the GEMM of sm89_fp8_linear (engine/kernels/sm89_fp8.py:444-528;
  * kernels _fp8_linear_kernel :220-300 and _fp8_split_gemm_kernel :343-398):
  *   y[m, n] = sum_kb dot(x8[m, kb], w8[n, kb]) * a_scale[kb][m] * w_scale[n / 128][kb]
- * with fp32 accumulation and K blocks in increasing order, y in bf16 or fp16.
+ * with fp32 accumulation, y in bf16 or fp16.
  * x8 [m, k] e4m3 (row stride ldx bytes), a_scale as mie_fp8_quantize writes it,
  * w8 [n, k] e4m3 (row stride ldw bytes), w_scale [ceil(n/128), w_scale_ld].
  * Operand base pointers and row strides must be multiples of 16 bytes.
  * Up to 128 tokens run with the weight rows as the 128 MMA rows (a weight
- * streaming loop); more tokens run a persistent 128 x 256-tile kernel.  When a
- * shape has fewer output tiles than SMs the K range of each tile is cut into
- * 2 or 4 parts that run as one thread-block cluster and are summed in a fixed
- * order through distributed shared memory; max_split > 0 caps that factor
- * (1 = never split), 0 lets the library choose.  trace is a profiling aid:
- * NULL, or a device buffer of 16 int64 per CTA that receives %globaltimer
- * stamps of the kernel's phases.  Uses no global scratch memory.
- * The weight tiles of the first pipeline stages are requested while the kernel
- * queued before this one may still be running (programmatic dependent launch):
- * w8 must not be written by that kernel (MIE_GEMM_PREFETCH=0 lifts this).
+ * streaming loop); more tokens run a persistent 128 x 256-tile kernel.
+ *
+ * Summation order.  Within one CTA the K blocks are added in increasing order.
+ * When a shape has fewer output tiles than SMs - or, above 128 tokens, when the
+ * tiles left over after the last whole round of SMs are few - the K range of a
+ * tile is cut into 2, 4 or 8 contiguous parts that run as one thread-block
+ * cluster; each part is summed in increasing K order and the parts are then
+ * added in part order through distributed shared memory.  That is a fixed
+ * order (results never depend on timing), but it is not the single increasing
+ * K order, and whether a tile is cut depends on m, n and the SM count, so a
+ * token's row can differ in the last bit between batch sizes.  max_split = 1
+ * never cuts: every output element is then the plain increasing-K sum,
+ * independent of the batch it was computed in (the reference's row-independence
+ * promise, tests/test_sm89_fp8_exact.py); max_split = 0 lets the library
+ * choose, other values cap the factor.  Uses no global scratch memory.
+ *
+ * flags: MIE_GEMM_NO_WEIGHT_PREFETCH, or 0.  By default the weight tiles of the
+ * first pipeline stages are requested while the kernel queued before this one
+ * may still be running (programmatic dependent launch), so w8 must not be
+ * written by that kernel; pass the flag (or set MIE_GEMM_PREFETCH=0) when it is.
  */
+#define MIE_GEMM_NO_WEIGHT_PREFETCH 1
 int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
                  int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy, int32_t out_dtype,
-                 int32_t m, int32_t n, int32_t k, int32_t max_split, int32_t* status, int64_t* trace, void* stream);
+                 int32_t m, int32_t n, int32_t k, int32_t max_split, int32_t flags, int32_t* status, void* stream);
 
 /* ------------------------------------------------------------------------
  * Fused memory-bound glue (bf16 activations)

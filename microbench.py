@@ -1,9 +1,9 @@
 """Single-kernel micro-benchmarks of the hot path (also the small cases profiled with ncu).
 
-    python -m mini_inference_engine_b200.microbench decode --concurrency 64
-    python -m mini_inference_engine_b200.microbench gemm --shape qkv --rows 256
-    python -m mini_inference_engine_b200.microbench prefill --requests 6
-    python -m mini_inference_engine_b200.microbench lm_head --rows 8
+    python microbench.py decode --concurrency 64
+    python microbench.py gemm --shape qkv --rows 256
+    python microbench.py prefill --requests 6
+    python microbench.py lm_head --rows 8
 
 Each prints one JSON line with the CUDA-event time per launch (median of the repeats, L2 flushed by a
 256 MiB fill between repeats) and the algorithmic bytes / FLOPs of the launch.
@@ -15,12 +15,25 @@ import argparse
 import json
 import statistics
 
+import sys
+from pathlib import Path
+
 import torch
 
-from . import _lib, workloads
-from .engine.kernels import sm89_fp8
-from .engine.kv_cache import triton_flash_prefill_attention, triton_write_packed_kv
-from .engine.kv_cache.triton_paged_attention import decode_scratch, launch_decode_attention
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+from mini_inference_engine_b200 import _lib, workloads  # noqa: E402
+from mini_inference_engine_b200.engine.kernels import sm89_fp8  # noqa: E402
+from mini_inference_engine_b200.engine.kv_cache import (  # noqa: E402
+    triton_flash_prefill_attention,
+    triton_write_packed_kv,
+)
+from mini_inference_engine_b200.engine.kv_cache.triton_paged_attention import (  # noqa: E402
+    decode_scratch,
+    launch_decode_attention,
+)
 
 
 def _time(run, repeats: int, device: torch.device) -> float:

@@ -21,6 +21,9 @@ STATUS_BAD_SEQUENCE = 8
 STATUS_WAIT_TIMEOUT = 16
 STATUS_MAX_LENGTH = 32
 STATUS_CAPACITY = 64
+STATUS_NO_TOKEN = 128
+
+GEMM_NO_WEIGHT_PREFETCH = 1
 
 STATUS_MESSAGES = {
     STATUS_BAD_LENGTH: "sequence_lengths exceed the available block-table capacity",
@@ -30,6 +33,7 @@ STATUS_MESSAGES = {
     STATUS_WAIT_TIMEOUT: "a bounded device-side wait timed out",
     STATUS_MAX_LENGTH: "max_sequence_length does not cover the attention read length",
     STATUS_CAPACITY: "decode work plan exceeded its scratch capacity",
+    STATUS_NO_TOKEN: "greedy sampling found no candidate for a row (token 0 was substituted)",
 }
 
 DTYPE_CODES = {torch.bfloat16: 0, torch.float16: 1, torch.float32: 2}
@@ -90,7 +94,7 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "mie_fp8_quantize": (ctypes.c_int, [c_void_p, c_int64, c_int32, c_void_p, c_int64, c_void_p, c_int32, c_int32,
                                         c_int32, c_void_p]),
     "mie_fp8_gemm": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_int32,
-                                    c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32, c_void_p,
+                                    c_void_p, c_int64, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                     c_void_p, c_void_p]),
     "mie_rms_norm": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                     c_void_p, c_int32, c_int32, c_int32, c_float, c_void_p]),

@@ -46,9 +46,7 @@ __device__ __forceinline__ void epi_bar_sync(int threads) {
 // Kernel
 // --------------------------------------------------------------------------
 struct GemmParams {
-  // Row operand rows / column operand rows (see the orientation note above).
-  int rows_r, rows_c, k;
-  int m, n;               // logical problem (tokens, weight rows)
+  int m, n, k;            // tokens, weight rows, reduction length
   const float* a_scale;   // [k_blocks][a_scale_ld]  (token scales, K-block major)
   int a_scale_ld;
   const float* w_scale;   // [ceil(n/128)][w_scale_ld]
@@ -57,33 +55,28 @@ struct GemmParams {
   long long ldy;
   int out_f16;
   int* status;
-  long long* trace;       // optional [CTAs][16] globaltimer stamps (profiling aid), or null
   int prefetch;           // weights of the first K blocks are requested before the launch-chain wait
+  // Wide kernel only: this launch covers output tiles [tile_begin, tile_end).  late_wait: the launch-chain
+  // wait is taken at the end of the kernel instead of the start (second launch of a two-launch GEMM, whose
+  // inputs are already known to be complete because the first launch waited for them).
+  int tile_begin, tile_end, late_wait;
 };
 
-__device__ __forceinline__ void trace_stamp(const GemmParams& p, int slot) {
-  if (p.trace != nullptr) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    p.trace[(size_t)(blockIdx.x * gridDim.y + blockIdx.y) * 16 + slot] = (long long)t;
-  }
-}
-
-// Scale staging: per chunk of kChunkKb K blocks the epilogue warps pull every
-// scale they will need into shared memory in one batch, so no global-memory
-// latency sits between two K blocks.
-template <int BN, bool kSwap>
+// Scale staging: per chunk of kChunkKb K blocks the promotion warps pull every
+// scale product they will need into shared memory in one batch, so no
+// global-memory latency sits between two K blocks.
+template <int BN>
 struct ScaleStage {
-  static constexpr int kWidth = kSwap ? BN : kTileR;             // token scales per K block
-  static constexpr int kChunkKb = kSwap ? (4096 / BN > 32 ? 32 : 4096 / BN) : 16;
-  static constexpr int kWBlocks = kSwap ? 1 : (BN + 127) / 128;  // weight scale blocks per tile column range
-  static constexpr int kFloats = kChunkKb * kWidth + kChunkKb * kWBlocks;
+  static constexpr int kChunkKb = 4096 / BN > 32 ? 32 : 4096 / BN;
+  static constexpr int kFloats = kChunkKb * BN;  // one a_scale * w_scale product per (K block, token)
 };
 
-template <int BN, int E, bool kSwap>
+constexpr int kNarrowEpiWarps = 4;  // promotion warps of fp8_gemm_kernel (one per TMEM lane quadrant)
+
+template <int BN>
 struct GemmSmem {
   static constexpr int kStageBytes = kTileR * kBlockK + BN * kBlockK;
-  static constexpr int kScaleBytes = ScaleStage<BN, kSwap>::kFloats * 4;
+  static constexpr int kScaleBytes = ScaleStage<BN>::kFloats * 4;
   // Narrow column tiles (few tokens) use few registers: two CTAs share an SM, which halves the cost of a
   // partial last wave and doubles the TMA requests in flight per SM.
   static constexpr int kCtasPerSm = BN <= 32 ? 2 : 1;
@@ -96,13 +89,6 @@ struct GemmSmem {
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-__device__ __forceinline__ float ld_peer_smem(uint32_t local_addr, uint32_t rank) {
-  uint32_t remote;
-  float v;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(rank));
-  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
-  return v;
-}
 
 // Largest split * ceil(chunks / split) over the allowed split factors (1..8).
 constexpr int max_reduction_chunks(int chunks) {
@@ -114,24 +100,30 @@ constexpr int max_reduction_chunks(int chunks) {
   return worst;
 }
 
-template <int BN, int E, bool kSwap>
-__global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
-    fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_r, const __grid_constant__ CUtensorMap map_c,
+__device__ __forceinline__ void store_out(const GemmParams& p, long long token, int col, float v) {
+  if (p.out_f16)
+    reinterpret_cast<__half*>(p.y)[token * p.ldy + col] = __float2half_rn(v);
+  else
+    reinterpret_cast<__nv_bfloat16*>(p.y)[token * p.ldy + col] = __float2bfloat16_rn(v);
+}
+
+// Up to 128 tokens.  The 128 UMMA rows are weight rows (one 128-row scale block per tile), the BN columns
+// are tokens.  Warps 0..3 promote, warp 4 is the TMA producer, warp 5 issues the MMAs and owns TMEM.
+// grid = (tiles, split), cluster = (1, split, 1): CTA `rank` of a cluster takes the rank-th part of K.
+template <int BN>
+__global__ void __launch_bounds__((kNarrowEpiWarps + 2) * 32, (BN <= 32 ? 2 : 1))
+    fp8_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GemmParams p) {
-  // Only the swapped orientation with four promotion warps is instantiated (up to 128 tokens); the token-major
-  // orientation of this template is kept as the reference form of the arithmetic, the product path for more
-  // tokens is fp8_gemm_wide_kernel.
-  static_assert(kSwap && E == 4, "more than 128 tokens run fp8_gemm_wide_kernel");
-  using S = GemmSmem<BN, E, kSwap>;
-  using SS = ScaleStage<BN, kSwap>;
+  using S = GemmSmem<BN>;
+  using SS = ScaleStage<BN>;
+  constexpr int E = kNarrowEpiWarps;
   constexpr int kStages = S::kStages;
-  constexpr int kCols = E == 8 ? BN / 2 : BN;  // accumulator columns owned by one epilogue warp
   // Accumulator ring in TMEM: as many BN-column buffers as fit (at most 8), so the MMA issuer can run
   // several K blocks ahead of the promotion.
   constexpr int kAcc = (512 / S::kCtasPerSm) / BN > 8 ? 8 : (512 / S::kCtasPerSm) / BN;
   constexpr uint32_t kTmemCols = kAcc * BN < 32 ? 32 : kAcc * BN;
   static_assert((kTmemCols & (kTmemCols - 1)) == 0 && kTmemCols <= 512, "TMEM columns must be a power of two <= 512");
-  static_assert(kCols % 16 == 0, "column slice must be a multiple of 16");
+  static_assert(BN % 16 == 0, "token tile must be a multiple of 16");
   // The stage ring doubles as the landing zone of the cluster reduction: split slots of ceil(BN/8/split)
   // 8-column chunks each, at most (BN/8 + 7) chunks in total.
   static_assert(kStages * S::kStageBytes >= max_reduction_chunks(BN / 8) * 8 * kTileR * 4,
@@ -144,14 +136,14 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full = empty_bar + kStages;
   uint64_t* tmem_empty = tmem_full + 8;
-  float* sscale = reinterpret_cast<float*>(tmem_empty + 8);  // staged scales of the current K chunk
+  float* sscale = reinterpret_cast<float*>(tmem_empty + 8);  // staged scale products of the current K chunk
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(sscale + SS::kFloats);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb_total = (p.k + kBlockK - 1) / kBlockK;
-  const int tiles_r = (p.rows_r + kTileR - 1) / kTileR;
-  const int split = gridDim.y, rank = blockIdx.y, tile = blockIdx.x;  // cluster = (1, split, 1)
-  const int tr = tile % tiles_r, tc = tile / tiles_r;
+  const int tiles_w = (p.n + kTileR - 1) / kTileR;
+  const int split = gridDim.y, rank = blockIdx.y, tile = blockIdx.x;
+  const int tw = tile % tiles_w, tt = tile / tiles_w;  // weight-row tile, token tile
   const int kb_first = (int)((long long)kb_total * rank / split);
   const int kb_last = (int)((long long)kb_total * (rank + 1) / split);  // exclusive
 
@@ -165,8 +157,8 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
       mbar_init(&tmem_empty[b], E);
     }
     mbar_fence_init();
-    tma_prefetch_desc(&map_r);
-    tma_prefetch_desc(&map_c);
+    tma_prefetch_desc(&map_w);
+    tma_prefetch_desc(&map_x);
   }
   if (warp == E + 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -177,41 +169,36 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   // Barriers, tensor-map prefetch and the TMEM allocation above overlap the tail of the previous kernel.
-  // So can the weights (nothing on the stream writes them): the producer requests the weight half of its
-  // first stages before the launch-chain wait and adds the activation half afterwards.
+  // So can the weights (the caller promises that the kernel queued before this one does not write them):
+  // the producer requests the weight half of its first stages before the launch-chain wait and adds the
+  // activation half afterwards.
   uint32_t prefetched = 0;
-  if (kSwap && p.prefetch && warp == E && lane == 0) {
+  if (p.prefetch && warp == E && lane == 0) {
     const uint64_t stream_policy = l2_evict_first_policy();
     for (int kb = kb_first; kb < kb_last && prefetched < (uint32_t)kStages; ++kb, ++prefetched) {
       mbar_expect_tx(&full_bar[prefetched], S::kStageBytes);
-      tma_load_2d_hint(stage_base + (size_t)prefetched * S::kStageBytes, &map_r, &full_bar[prefetched], kb * kBlockK,
-                       tr * kTileR, stream_policy);
+      tma_load_2d_hint(stage_base + (size_t)prefetched * S::kStageBytes, &map_w, &full_bar[prefetched], kb * kBlockK,
+                       tw * kTileR, stream_policy);
     }
   }
   chain_wait();
   chain_release();
-  if (threadIdx.x == 0) {
-    trace_stamp(p, 0);
-    trace_stamp(p, 1);
-  }
 
-  // Epilogue state that outlives the role branch (the reduction below needs it).
+  // Promotion state that outlives the role branch (the reduction below needs it).
   constexpr int kEpiThreads = E * 32;
-  const int quad = warp & 3, half = E == 8 ? (warp >> 2) & 1 : 0;
-  const int row_in_tile = quad * 32 + lane;
-  const int col0 = half * kCols;
-  float acc[kCols];
+  const int row_in_tile = (warp & 3) * 32 + lane;
+  float acc[BN];
 
   if (warp == E) {
     // ---------------- TMA producer ----------------
     if (lane == 0) {
-      const uint64_t stream_policy = l2_evict_first_policy();
+      const uint64_t stream_policy = l2_evict_first_policy();  // weights are streamed once per call
       uint32_t n = 0;
       for (int kb = kb_first; kb < kb_last; ++kb, ++n) {
         const int s = n % kStages;
         uint8_t* dst = stage_base + (size_t)s * S::kStageBytes;
         if (n < prefetched) {  // the weight half is already on its way
-          tma_load_2d(dst + kTileR * kBlockK, &map_c, &full_bar[s], kb * kBlockK, tc * BN);
+          tma_load_2d(dst + kTileR * kBlockK, &map_x, &full_bar[s], kb * kBlockK, tt * BN);
           continue;
         }
         if (!mbar_wait_bounded(&empty_bar[s], ((n / kStages) & 1u) ^ 1u)) {
@@ -219,14 +206,9 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
           break;
         }
         mbar_expect_tx(&full_bar[s], S::kStageBytes);
-        if (kSwap)  // decode-time weights are streamed once: keep them from flushing L2
-          tma_load_2d_hint(dst, &map_r, &full_bar[s], kb * kBlockK, tr * kTileR, stream_policy);
-        else
-          tma_load_2d(dst, &map_r, &full_bar[s], kb * kBlockK, tr * kTileR);
-        tma_load_2d(dst + kTileR * kBlockK, &map_c, &full_bar[s], kb * kBlockK, tc * BN);
-        if (n == 0) trace_stamp(p, 2);
+        tma_load_2d_hint(dst, &map_w, &full_bar[s], kb * kBlockK, tw * kTileR, stream_policy);
+        tma_load_2d(dst + kTileR * kBlockK, &map_x, &full_bar[s], kb * kBlockK, tt * BN);
       }
-      trace_stamp(p, 3);
     }
   } else if (warp == E + 1) {
     // ---------------- MMA issuer ----------------
@@ -241,7 +223,6 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
           break;
         }
         tc_fence_after();
-        if (n == 0) trace_stamp(p, 4);
         const uint32_t a_addr = smem_u32(stage_base + (size_t)s * S::kStageBytes);
         const uint32_t b_addr = a_addr + kTileR * kBlockK;
         const uint64_t da = smem_desc_k128(a_addr), db = smem_desc_k128(b_addr);
@@ -251,143 +232,84 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
                   k > 0 ? 1u : 0u);
         }
         umma_commit(&empty_bar[s]);  // frees the smem stage once these MMAs have read it
-        umma_commit(&tmem_full[b]);  // hands the K block's accumulator to the epilogue
+        umma_commit(&tmem_full[b]);  // hands the K block's accumulator to the promotion warps
       }
-      trace_stamp(p, 5);
     }
   } else {
-    // ---------------- Epilogue warps: promote every K block with its scales ----------------
-    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    const int epi_tid = threadIdx.x;  // epilogue warps are warps 0..E-1
-    const int wblk = tr;              // swapped mode: the tile's 128 weight rows are one scale block
+    // ---------------- Promotion warps: add every K block with its scales ----------------
+    const uint32_t lane_addr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const int epi_tid = threadIdx.x;  // promotion warps are warps 0..E-1
     uint32_t n = 0;
     bool ok = true;
 #pragma unroll
-    for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
+    for (int j = 0; j < BN; ++j) acc[j] = 0.f;
     for (int kb0 = kb_first; kb0 < kb_last && ok; kb0 += SS::kChunkKb) {
       const int kc = kb_last - kb0 < SS::kChunkKb ? kb_last - kb0 : SS::kChunkKb;
-      // Stage this chunk's scales (all loads in flight together).
+      // Stage this chunk's scale products a_scale[token] * w_scale (all loads in flight together).
       epi_bar_sync(kEpiThreads);  // the previous chunk's readers are done
-      float* s_w = sscale + SS::kChunkKb * SS::kWidth;
-      if (kSwap) {
-        // Products a_scale[token] * w_scale, one per (K block, column).
-        for (int i = epi_tid; i < kc * BN; i += kEpiThreads) {
-          const int kk = i / BN, tok = tc * BN + i % BN;
-          const float ws = p.w_scale[(long long)wblk * p.w_scale_ld + kb0 + kk];
-          sscale[i] = tok < p.m ? p.a_scale[(long long)(kb0 + kk) * p.a_scale_ld + tok] * ws : 0.f;
-        }
-      } else {
-        for (int i = epi_tid; i < kc * kTileR; i += kEpiThreads) {
-          const int kk = i / kTileR, tok = tr * kTileR + i % kTileR;
-          sscale[i] = tok < p.m ? p.a_scale[(long long)(kb0 + kk) * p.a_scale_ld + tok] : 0.f;
-        }
-        for (int i = epi_tid; i < kc * SS::kWBlocks; i += kEpiThreads) {
-          const int kk = i / SS::kWBlocks, blk = (tc * BN) / 128 + i % SS::kWBlocks;
-          s_w[i] = blk * 128 < p.n ? p.w_scale[(long long)blk * p.w_scale_ld + kb0 + kk] : 0.f;
-        }
+      for (int i = epi_tid; i < kc * BN; i += kEpiThreads) {
+        const int kk = i / BN, tok = tt * BN + i % BN;
+        const float ws = p.w_scale[(long long)tw * p.w_scale_ld + kb0 + kk];
+        sscale[i] = tok < p.m ? p.a_scale[(long long)(kb0 + kk) * p.a_scale_ld + tok] * ws : 0.f;
       }
       epi_bar_sync(kEpiThreads);
-      if (epi_tid == 0 && n == 0) trace_stamp(p, 6);
       for (int kk = 0; kk < kc; ++kk, ++n) {
         const int b = n % kAcc;
-        float s_row = 0.f;
-        if (!kSwap) s_row = sscale[kk * kTileR + row_in_tile] * s_w[kk * SS::kWBlocks + (col0 / 128)];
-        const float* s_col = sscale + kk * BN + col0;  // swapped mode: one product per column
+        const float* s_col = sscale + kk * BN;
         if (!mbar_wait_bounded(&tmem_full[b], (n / kAcc) & 1u)) {
           raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
           ok = false;
           break;
         }
         tc_fence_after();
-        if (epi_tid == 0 && n == 0) trace_stamp(p, 7);
-        const uint32_t taddr = lane_addr + (uint32_t)(b * BN + col0);
-        if constexpr (kCols % 64 == 0) {
+        const uint32_t taddr = lane_addr + (uint32_t)(b * BN);
+        if constexpr (BN % 64 == 0) {
           // Two loads in flight per wait: halves the TMEM round trips per K block.
 #pragma unroll
-          for (int c = 0; c < kCols; c += 64) {
+          for (int c = 0; c < BN; c += 64) {
             float d0[32], d1[32];
             tmem_ld32(taddr + c, d0);
             tmem_ld32(taddr + c + 32, d1);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(d0[j], kSwap ? s_col[c + j] : s_row, acc[c + j]);
+            for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(d0[j], s_col[c + j], acc[c + j]);
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              acc[c + 32 + j] = fmaf(d1[j], kSwap ? s_col[c + 32 + j] : s_row, acc[c + 32 + j]);
+            for (int j = 0; j < 32; ++j) acc[c + 32 + j] = fmaf(d1[j], s_col[c + 32 + j], acc[c + 32 + j]);
           }
-        } else if constexpr (kCols % 32 == 0) {
+        } else if constexpr (BN % 32 == 0) {
+          float d[32];
+          tmem_ld32(taddr, d);
+          tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < kCols; c += 32) {
-            float d[32];
-            tmem_ld32(taddr + c, d);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) acc[c + j] = fmaf(d[j], kSwap ? s_col[c + j] : s_row, acc[c + j]);
-          }
+          for (int j = 0; j < 32; ++j) acc[j] = fmaf(d[j], s_col[j], acc[j]);
         } else {
           float d[16];
           tmem_ld16(taddr, d);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc[j] = fmaf(d[j], kSwap ? s_col[j] : s_row, acc[j]);
+          for (int j = 0; j < 16; ++j) acc[j] = fmaf(d[j], s_col[j], acc[j]);
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&tmem_empty[b]);
       }
     }
-    if (epi_tid == 0) trace_stamp(p, 8);
   }
 
   // ---------------- output: direct (split == 1) or reduced across the cluster ----------------
-  const int r_glob = tr * kTileR + row_in_tile;  // token (normal) or weight row (swapped)
+  const int w_row = tw * kTileR + row_in_tile;  // weight row = output column
   if (split == 1) {
-    if (warp < E) {
-      if (kSwap) {
-        if (r_glob < p.n) {
+    if (warp < E && w_row < p.n) {
 #pragma unroll
-          for (int j = 0; j < kCols; ++j) {
-            const int tok = tc * BN + col0 + j;
-            if (tok < p.m) {
-              if (p.out_f16)
-                reinterpret_cast<__half*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2half_rn(acc[j]);
-              else
-                reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2bfloat16_rn(acc[j]);
-            }
-          }
-        }
-      } else if (r_glob < p.m) {
-        const int n0 = tc * BN + col0;
-        uint16_t* yrow = reinterpret_cast<uint16_t*>(p.y) + (long long)r_glob * p.ldy + n0;
-        const bool vec = (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) && (n0 + kCols <= p.n);
-        if (vec) {
-#pragma unroll
-          for (int j = 0; j < kCols; j += 8) {
-            uint32_t w[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              w[q] = p.out_f16 ? Mma16816<__half>::pack(acc[j + 2 * q], acc[j + 2 * q + 1])
-                               : Mma16816<__nv_bfloat16>::pack(acc[j + 2 * q], acc[j + 2 * q + 1]);
-            }
-            *reinterpret_cast<uint4*>(yrow + j) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < kCols; ++j) {
-            if (n0 + j < p.n) {
-              if (p.out_f16)
-                reinterpret_cast<__half*>(yrow)[j] = __float2half_rn(acc[j]);
-              else
-                reinterpret_cast<__nv_bfloat16*>(yrow)[j] = __float2bfloat16_rn(acc[j]);
-            }
-          }
-        }
+      for (int j = 0; j < BN; ++j) {
+        const int tok = tt * BN + j;
+        if (tok < p.m) store_out(p, tok, w_row, acc[j]);
       }
     }
   } else {
-    // Every MMA of this CTA has completed (the epilogue consumed the last accumulator), so the stage ring
-    // is free.  Rank d owns the 8-column chunks [d * slice, (d + 1) * slice) of the tile: every CTA pushes
-    // its partial of those columns into slot [its own rank] of the owner's ring (remote shared-memory
+    // Every MMA of this CTA has completed (the promotion consumed the last accumulator), so the stage ring
+    // is free.  Rank d owns the 8-token chunks [d * slice, (d + 1) * slice) of the tile: every CTA pushes
+    // its partial of those tokens into slot [its own rank] of the owner's ring (remote shared-memory
     // stores), the cluster barrier publishes them, and the owner adds the slots in rank order.
     constexpr int kChunks = BN / 8;
     const int slice = (kChunks + split - 1) / split;            // chunks per owner
@@ -396,21 +318,20 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
     cluster_sync_all();  // every CTA of the cluster is done with its own stage ring
     if (warp < E) {
 #pragma unroll
-      for (int j = 0; j < kCols; ++j) {
-        const int col = col0 + j, owner = (col >> 3) / slice;
-        const int local_col = col - owner * slice * 8;
+      for (int j = 0; j < BN; ++j) {
+        const int owner = (j >> 3) / slice;
+        const int local_col = j - owner * slice * 8;
         const uint32_t local = red_addr + (uint32_t)((rank * slice_floats + local_col * kTileR + row_in_tile) * 4);
         uint32_t remote;
         asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"((uint32_t)owner));
         asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(acc[j]) : "memory");
       }
     }
-    if (threadIdx.x == 0) trace_stamp(p, 9);
     cluster_sync_all();
     if (warp < E) {
       const float* red = reinterpret_cast<const float*>(stage_base);
       const int chunk_lo = rank * slice, chunk_hi = (rank + 1) * slice < kChunks ? (rank + 1) * slice : kChunks;
-      for (int ch = chunk_lo + (E == 8 ? (warp >> 2) : 0); ch < chunk_hi; ch += (E == 8 ? 2 : 1)) {
+      for (int ch = chunk_lo; ch < chunk_hi; ++ch) {
         float sum[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) sum[j] = 0.f;
@@ -419,49 +340,17 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
           for (int j = 0; j < 8; ++j)
             sum[j] += red[peer * slice_floats + ((ch - chunk_lo) * 8 + j) * kTileR + row_in_tile];
         }
-        if (kSwap) {
-          if (r_glob < p.n) {
+        if (w_row < p.n) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const int tok = tc * BN + ch * 8 + j;
-              if (tok < p.m) {
-                if (p.out_f16)
-                  reinterpret_cast<__half*>(p.y)[(long long)tok * p.ldy + r_glob] = __float2half_rn(sum[j]);
-                else
-                  reinterpret_cast<__nv_bfloat16*>(p.y)[(long long)tok * p.ldy + r_glob] =
-                      __float2bfloat16_rn(sum[j]);
-              }
-            }
-          }
-        } else if (r_glob < p.m) {
-          const int n0 = tc * BN + ch * 8;
-          uint16_t* yrow = reinterpret_cast<uint16_t*>(p.y) + (long long)r_glob * p.ldy + n0;
-          const bool vec = (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) && (n0 + 8 <= p.n);
-          if (vec) {
-            uint32_t w[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              w[q] = p.out_f16 ? Mma16816<__half>::pack(sum[2 * q], sum[2 * q + 1])
-                               : Mma16816<__nv_bfloat16>::pack(sum[2 * q], sum[2 * q + 1]);
-            }
-            *reinterpret_cast<uint4*>(yrow) = make_uint4(w[0], w[1], w[2], w[3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              if (n0 + j < p.n) {
-                if (p.out_f16)
-                  reinterpret_cast<__half*>(yrow)[j] = __float2half_rn(sum[j]);
-                else
-                  reinterpret_cast<__nv_bfloat16*>(yrow)[j] = __float2bfloat16_rn(sum[j]);
-              }
-            }
+          for (int j = 0; j < 8; ++j) {
+            const int tok = tt * BN + ch * 8 + j;
+            if (tok < p.m) store_out(p, tok, w_row, sum[j]);
           }
         }
       }
     }
     // No CTA reads a peer after the barrier above, so nothing more is needed before exit.
   }
-  if (threadIdx.x == 0) trace_stamp(p, 11);
 
   tc_fence_before();
   __syncthreads();
@@ -469,7 +358,6 @@ __global__ void __launch_bounds__((E + 2) * 32, (BN <= 32 ? 2 : 1))
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
   }
-  if (threadIdx.x == 0) trace_stamp(p, 12);
 }
 
 // --------------------------------------------------------------------------
@@ -506,11 +394,12 @@ struct WideItem {
   int tm, tn, k0, k1;
 };
 
-// Work of CTA (x, rank) of a (gridDim.x, split) grid.  split == 1: tiles x, x + gridDim.x, ... whole.
-// split > 1 (one cluster per tile): tile x, the rank-th part of its K range.
-__device__ __forceinline__ bool wide_item(int tiles, int tiles_m, int kb_total, int split, int rank, int idx,
-                                          WideItem& it) {
-  const int tile = blockIdx.x + idx * gridDim.x;
+// Work of CTA (x, rank) of a (gridDim.x, split) grid over the tiles [first, tiles).  split == 1: tiles
+// first + x, first + x + gridDim.x, ... whole.  split > 1 (one cluster per tile): tile first + x, the
+// rank-th part of its K range.
+__device__ __forceinline__ bool wide_item(int first, int tiles, int tiles_m, int kb_total, int split, int rank,
+                                          int idx, WideItem& it) {
+  const int tile = first + blockIdx.x + idx * gridDim.x;
   if (tile >= tiles || (split > 1 && idx > 0)) return false;
   it.tm = tile % tiles_m;
   it.tn = tile / tiles_m;
@@ -557,14 +446,6 @@ __device__ __forceinline__ void promote32(float* acc, const float (&d)[32], floa
     const float2 r = __ffma2_rn(make_float2(d[j], d[j + 1]), s2, make_float2(acc[j], acc[j + 1]));
     acc[j] = r.x;
     acc[j + 1] = r.y;
-  }
-}
-
-__device__ __forceinline__ void wide_stamp(const GemmParams& p, int slot) {
-  if (p.trace != nullptr) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    p.trace[(size_t)(blockIdx.x * gridDim.y + blockIdx.y) * 16 + slot] = (long long)t;
   }
 }
 
@@ -643,7 +524,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb_total = (p.k + kBlockK - 1) / kBlockK;
   const int tiles_m = (p.m + kTileR - 1) / kTileR;
-  const int tiles = tiles_m * ((p.n + BN - 1) / BN);
+  const int tiles = p.tile_end;
   const int split = gridDim.y, rank = blockIdx.y;  // cluster = (1, split, 1)
 
   if (threadIdx.x == 0) {
@@ -673,7 +554,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   uint32_t prefetched = 0;
   if (p.prefetch && warp == E && lane == 0) {
     WideItem first;
-    if (wide_item(tiles, tiles_m, kb_total, split, rank, 0, first)) {
+    if (wide_item(p.tile_begin, tiles, tiles_m, kb_total, split, rank, 0, first)) {
       for (int kb = first.k0; kb < first.k1 && prefetched < (uint32_t)kStages; ++kb, ++prefetched) {
         mbar_expect_tx(&full_bar[prefetched], kWideStageBytes);
         tma_load_2d(stage_base + (size_t)prefetched * kWideStageBytes + kTileR * kBlockK, &map_w,
@@ -681,15 +562,14 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       }
     }
   }
-  chain_wait();
+  if (!p.late_wait) chain_wait();
   chain_release();
-  if (threadIdx.x == 0) wide_stamp(p, 0);
 
   // K blocks this CTA will process (the promotion pipeline needs to know when the last one is reached).
   uint32_t total_blocks = 0;
   {
     WideItem it;
-    for (int idx = 0; wide_item(tiles, tiles_m, kb_total, split, rank, idx, it); ++idx) total_blocks += (uint32_t)(it.k1 - it.k0);
+    for (int idx = 0; wide_item(p.tile_begin, tiles, tiles_m, kb_total, split, rank, idx, it); ++idx) total_blocks += (uint32_t)(it.k1 - it.k0);
   }
 
   if (warp >= E) {
@@ -699,7 +579,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       uint32_t n = 0;
       bool ok = true;
       WideItem it;
-      for (int idx = 0; ok && wide_item(tiles, tiles_m, kb_total, split, rank, idx, it); ++idx) {
+      for (int idx = 0; ok && wide_item(p.tile_begin, tiles, tiles_m, kb_total, split, rank, idx, it); ++idx) {
         for (int kb = it.k0; kb < it.k1; ++kb, ++n) {
           const int s = n % kStages;
           uint8_t* dst = stage_base + (size_t)s * kWideStageBytes;
@@ -768,10 +648,9 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         tmem_ld32(lane_addr, buf_a);
         tmem_ld32(lane_addr + 32, buf_b);
       }
-      if (epi_tid == 0) wide_stamp(p, 1);
     }
     WideItem it;
-    for (int idx = 0; ok && wide_item(tiles, tiles_m, kb_total, split, rank, idx, it); ++idx) {
+    for (int idx = 0; ok && wide_item(p.tile_begin, tiles, tiles_m, kb_total, split, rank, idx, it); ++idx) {
       const int tok0 = it.tm * kTileR;
       for (int kb0 = it.k0; kb0 < it.k1 && ok; kb0 += kWideChunkKb) {
         const int kc = it.k1 - kb0 < kWideChunkKb ? it.k1 - kb0 : kWideChunkKb;
@@ -817,7 +696,6 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         }
       }
       if (!ok) break;
-      if (epi_tid == 0) wide_stamp(p, 2);
 
       const int r_glob = tok0 + row_in_tile;
       if (split == 1) {
@@ -877,17 +755,13 @@ __global__ void __launch_bounds__(kWideThreads, 1)
           const int g = (col0 + j) >> 2;
           park[row_in_tile * 64 + (g ^ (row_in_tile & 7))] = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
         }
-        if (epi_tid == 0) wide_stamp(p, 3);
         cluster_sync_all();
-        if (epi_tid == 0) wide_stamp(p, 8);
         if (split == 2)
           wide_cluster_reduce<2>(p, smem_u32(stage_base), rank, epi_tid, tok0, it.tn * BN);
         else
           wide_cluster_reduce<4>(p, smem_u32(stage_base), rank, epi_tid, tok0, it.tn * BN);
-        if (epi_tid == 0) wide_stamp(p, 4);
         cluster_sync_all();  // no CTA leaves while a peer may still read its partial
       }
-      if (epi_tid == 0) wide_stamp(p, 5);
 #pragma unroll
       for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
     }
@@ -900,15 +774,14 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     }
   }
 
+  // Second launch of a two-launch GEMM: it ran beside the first one, and must not complete before it
+  // (the kernel queued behind only waits for this one).
+  if (p.late_wait) chain_wait();
   tc_fence_before();
   __syncthreads();
   if (warp == E + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
-  }
-  if (threadIdx.x == 0) {
-    if (p.trace != nullptr) p.trace[(size_t)(blockIdx.x * gridDim.y + blockIdx.y) * 16 + 7] = (long long)total_blocks;
-    wide_stamp(p, 6);
   }
 }
 
@@ -1035,15 +908,16 @@ int choose_split(long long tiles, int kb_total, int bn, int ctas_per_sm, int max
   return best;
 }
 
-template <int BN, int E, bool kSwap>
-int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& p, long long tiles, int split,
+template <int BN>
+int launch_gemm(const CUtensorMap& mw, const CUtensorMap& mx, const GemmParams& p, long long tiles, int split,
                 cudaStream_t stream) {
-  using S = GemmSmem<BN, E, kSwap>;
+  using S = GemmSmem<BN>;
+  constexpr int E = kNarrowEpiWarps;
   static bool configured[64] = {false};
   int dev = 0;
   MIE_CUDA(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !configured[dev]) {
-    MIE_CUDA(cudaFuncSetAttribute(fp8_gemm_kernel<BN, E, kSwap>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    MIE_CUDA(cudaFuncSetAttribute(fp8_gemm_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                   S::kTotal));
     configured[dev] = true;
   }
@@ -1061,7 +935,7 @@ int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& 
   attr[0].val.clusterDim.z = 1;
   config.attrs = attr;
   config.numAttrs = chained_launch_enabled() ? 2 : 1;
-  MIE_CUDA(cudaLaunchKernelEx(&config, fp8_gemm_kernel<BN, E, kSwap>, mr, mc, p));
+  MIE_CUDA(cudaLaunchKernelEx(&config, fp8_gemm_kernel<BN>, mw, mx, p));
   MIE_LAUNCH_CHECK("fp8_gemm_kernel");
   return MIE_OK;
 }
@@ -1069,41 +943,59 @@ int launch_gemm(const CUtensorMap& mr, const CUtensorMap& mc, const GemmParams& 
 // Column-tile width for the swapped orientation: smallest of 16/32/64/128 covering m.
 int swap_bn(int m) { return m <= 16 ? 16 : m <= 32 ? 32 : m <= 64 ? 64 : 128; }
 
-// Schedule of the wide kernel for `tiles` output tiles of `kb` K blocks: persistent whole tiles (split 1)
-// or one tile per `split`-CTA cluster.  Costs in units of one K block of the main loop; the cluster
-// reduction and the fill / drain of a CTA are worth a few blocks each.
-int choose_wide_split(long long tiles, int kb, int max_split) {
+// Schedule of the wide kernel.  `tiles` output tiles of `kb` K blocks on P SMs (one 200 KB CTA each):
+//   tiles <= P      one launch; whole tiles, or one tile per 2-/4-CTA cluster with the K range cut when all
+//                   clusters still fit one wave;
+//   tiles > P       the whole waves (floor(tiles / P) * P tiles) run as one persistent launch; the
+//                   remaining R tiles would otherwise cost a full extra round on R of the P SMs, so when
+//                   R * s <= P they go to a second launch of one s-CTA cluster per tile (s = 2 or 4) that
+//                   starts on the SMs the first launch frees and finishes in 1 / s of a round.
+// Costs in units of one K block of the main loop; the cluster reduction and the fill / drain of a CTA are
+// worth a few blocks each.
+struct WidePlan {
+  int main_tiles;  // tiles of the persistent launch (0: none)
+  int main_split;  // K split of the main launch (> 1 only when it is the only launch)
+  int tail_split;  // K split of the tail launch (0: no tail launch)
+};
+
+WidePlan plan_wide(long long tiles, int kb, int max_split) {
   const int slots = sm_count();
-  int best = 1;
-  double best_cost = 1e30;
-  for (int s = 1; s <= 4; s *= 2) {
-    if (s > kb || (max_split > 0 && s > max_split)) break;
-    if (s > 1 && tiles * s > slots) break;  // clusters only when all of them run in one wave
-    const double rounds = (double)((tiles * s + slots - 1) / slots);
-    const double cost = rounds * ((kb + s - 1) / s) + 4.0 + (s > 1 ? 3.0 : 0.0);
+  WidePlan plan{(int)tiles, 1, 0};
+  if (tiles <= slots) {
+    double best_cost = 1e30;
+    for (int s = 1; s <= 4; s *= 2) {
+      if (s > kb || (max_split > 0 && s > max_split)) break;
+      if (s > 1 && tiles * s > slots) break;  // clusters only when all of them run in one wave
+      const double cost = (double)((kb + s - 1) / s) + 4.0 + (s > 1 ? 3.0 : 0.0);
+      if (cost < best_cost - 1e-9) {
+        best_cost = cost;
+        plan.main_split = s;
+      }
+    }
+    return plan;
+  }
+  const long long rest = tiles % slots;
+  if (rest == 0) return plan;
+  double best_cost = (double)kb;  // the tail as one more whole round of the persistent launch
+  for (int s = 2; s <= 4; s *= 2) {
+    if (s > kb || (max_split > 0 && s > max_split) || rest * s > slots) break;
+    const double cost = (double)((kb + s - 1) / s) + 3.0 + 2.0;  // reduction + the second launch's start-up
     if (cost < best_cost - 1e-9) {
       best_cost = cost;
-      best = s;
+      plan.main_tiles = (int)(tiles - rest);
+      plan.tail_split = s;
     }
   }
-  return best;
+  return plan;
 }
 
-int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, const GemmParams& p, int max_split,
-                cudaStream_t stream) {
-  static bool configured[64] = {false};
-  int dev = 0;
-  MIE_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !configured[dev]) {
-    MIE_CUDA(cudaFuncSetAttribute(fp8_gemm_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  kWideSmemBytes));
-    configured[dev] = true;
-  }
-  const int kb = (p.k + kBlockK - 1) / kBlockK;
-  const long long tiles = (long long)((p.m + kTileR - 1) / kTileR) * ((p.n + kWideBN - 1) / kWideBN);
-  MIE_CHECK_ARG(tiles <= 0x7fffffff, "too many output tiles (%lld)", tiles);
-  const int split = choose_wide_split(tiles, kb, max_split);
-  const long long ctas = split > 1 ? tiles : (tiles < sm_count() ? tiles : sm_count());
+int launch_wide_range(const CUtensorMap& mx, const CUtensorMap& mw, GemmParams p, int tile_begin, int tile_end,
+                      int split, bool late_wait, cudaStream_t stream) {
+  p.tile_begin = tile_begin;
+  p.tile_end = tile_end;
+  p.late_wait = late_wait ? 1 : 0;
+  const int count = tile_end - tile_begin;
+  const int ctas = split > 1 ? count : (count < sm_count() ? count : sm_count());
   cudaLaunchConfig_t config = {};
   config.gridDim = dim3((unsigned)ctas, (unsigned)split, 1);
   config.blockDim = dim3(kWideThreads, 1, 1);
@@ -1120,6 +1012,30 @@ int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, const GemmParams& 
   config.numAttrs = chained_launch_enabled() ? 2 : 1;
   MIE_CUDA(cudaLaunchKernelEx(&config, fp8_gemm_wide_kernel, mx, mw, p));
   MIE_LAUNCH_CHECK("fp8_gemm_wide_kernel");
+  return MIE_OK;
+}
+
+int launch_wide(const CUtensorMap& mx, const CUtensorMap& mw, const GemmParams& p, int max_split,
+                cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  MIE_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    MIE_CUDA(cudaFuncSetAttribute(fp8_gemm_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  kWideSmemBytes));
+    configured[dev] = true;
+  }
+  const int kb = (p.k + kBlockK - 1) / kBlockK;
+  const long long tiles = (long long)((p.m + kTileR - 1) / kTileR) * ((p.n + kWideBN - 1) / kWideBN);
+  MIE_CHECK_ARG(tiles <= 0x7fffffff, "too many output tiles (%lld)", tiles);
+  const WidePlan plan = plan_wide(tiles, kb, max_split);
+  if (int rc = launch_wide_range(mx, mw, p, 0, plan.main_tiles, plan.main_split, false, stream)) return rc;
+  if (plan.tail_split > 0) {
+    // Only with launch chaining on does the tail start before the main launch has drained; without it the
+    // stream simply runs the two launches one after the other.
+    return launch_wide_range(mx, mw, p, plan.main_tiles, (int)tiles, plan.tail_split, chained_launch_enabled(),
+                             stream);
+  }
   return MIE_OK;
 }
 
@@ -1149,8 +1065,8 @@ extern "C" int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void*
 
 extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
                             int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy,
-                            int32_t out_dtype, int32_t m, int32_t n, int32_t k, int32_t max_split, int32_t* status,
-                            int64_t* trace, void* stream_) {
+                            int32_t out_dtype, int32_t m, int32_t n, int32_t k, int32_t max_split, int32_t flags,
+                            int32_t* status, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
   MIE_CHECK_ARG(x8 && a_scale && w8 && w_scale && y, "null pointer");
   MIE_CHECK_ARG(m >= 0 && n >= 1 && k >= 1, "invalid GEMM shape %d x %d x %d", m, n, k);
@@ -1159,26 +1075,19 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
   MIE_CHECK_ARG(((reinterpret_cast<uintptr_t>(x8) | reinterpret_cast<uintptr_t>(w8)) & 15) == 0,
                 "operands must be 16-byte aligned");
   MIE_CHECK_ARG(ldy >= n && a_scale_ld >= m && w_scale_ld >= (k + 127) / 128, "invalid leading dimension");
+  MIE_CHECK_ARG((flags & ~(MIE_GEMM_NO_WEIGHT_PREFETCH)) == 0, "unknown flag bits %d", flags);
   if (m == 0) return MIE_OK;
 
-  // Up to 128 tokens stream the weights through the swapped kernel, unless that needs a second wave of
+  // Up to 128 tokens stream the weights through the narrow kernel, unless that needs a second wave of
   // full-K tiles (more 128-row weight tiles than SMs at more than 32 tokens, where only one of its CTAs
   // fits an SM: gate_up): the wide kernel's 256-row tiles then finish in one round.
-  const bool swap = m <= 128 && !(m > 32 && (n + kTileR - 1) / kTileR > sm_count());
-  const int bn = swap ? swap_bn(m) : 256;
+  const bool narrow = m <= 128 && !(m > 32 && (n + kTileR - 1) / kTileR > sm_count());
   const int kb = (k + kBlockK - 1) / kBlockK;
-  const long long tiles_r = swap ? (n + kTileR - 1) / kTileR : (m + kTileR - 1) / kTileR;
-  const long long tiles_c = swap ? (m + bn - 1) / bn : (n + bn - 1) / bn;
-  const long long tiles = tiles_r * tiles_c;
-  MIE_CHECK_ARG(tiles <= 0x7fffffff, "too many output tiles (%lld)", tiles);
-  const int split = choose_split(tiles, kb, bn, bn <= 32 ? 2 : 1, max_split);
 
   GemmParams p;
-  p.rows_r = swap ? n : m;
-  p.rows_c = swap ? m : n;
-  p.k = k;
   p.m = m;
   p.n = n;
+  p.k = k;
   p.a_scale = a_scale;
   p.a_scale_ld = a_scale_ld;
   p.w_scale = w_scale;
@@ -1187,25 +1096,29 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
   p.ldy = ldy;
   p.out_f16 = out_dtype == MIE_DTYPE_F16;
   p.status = status;
-  p.trace = reinterpret_cast<long long*>(trace);
   static const int prefetch = [] {
     const char* v = getenv("MIE_GEMM_PREFETCH");
     return v != nullptr && v[0] == '0' ? 0 : 1;  // MIE_GEMM_PREFETCH=0 turns it off
   }();
-  p.prefetch = prefetch;
+  p.prefetch = prefetch && !(flags & MIE_GEMM_NO_WEIGHT_PREFETCH);
+  p.tile_begin = p.tile_end = p.late_wait = 0;
 
-  CUtensorMap mr, mc;
-  if (swap) {
-    if (int rc = operand_map(w8, n, k, ldw, kTileR, &mr)) return rc;
-    if (int rc = operand_map(x8, m, k, ldx, bn, &mc)) return rc;
+  CUtensorMap mw, mx;
+  if (narrow) {
+    const int bn = swap_bn(m);
+    const long long tiles = (long long)((n + kTileR - 1) / kTileR) * ((m + bn - 1) / bn);
+    MIE_CHECK_ARG(tiles <= 0x7fffffff, "too many output tiles (%lld)", tiles);
+    const int split = choose_split(tiles, kb, bn, bn <= 32 ? 2 : 1, max_split);
+    if (int rc = operand_map(w8, n, k, ldw, kTileR, &mw)) return rc;
+    if (int rc = operand_map(x8, m, k, ldx, bn, &mx)) return rc;
     switch (bn) {
-      case 16: return launch_gemm<16, 4, true>(mr, mc, p, tiles, split, stream);
-      case 32: return launch_gemm<32, 4, true>(mr, mc, p, tiles, split, stream);
-      case 64: return launch_gemm<64, 4, true>(mr, mc, p, tiles, split, stream);
-      default: return launch_gemm<128, 4, true>(mr, mc, p, tiles, split, stream);
+      case 16: return launch_gemm<16>(mw, mx, p, tiles, split, stream);
+      case 32: return launch_gemm<32>(mw, mx, p, tiles, split, stream);
+      case 64: return launch_gemm<64>(mw, mx, p, tiles, split, stream);
+      default: return launch_gemm<128>(mw, mx, p, tiles, split, stream);
     }
   }
-  if (int rc = operand_map(x8, m, k, ldx, kTileR, &mr)) return rc;
-  if (int rc = operand_map(w8, n, k, ldw, kWideBN, &mc)) return rc;
-  return launch_wide(mr, mc, p, max_split, stream);
+  if (int rc = operand_map(x8, m, k, ldx, kTileR, &mx)) return rc;
+  if (int rc = operand_map(w8, n, k, ldw, kWideBN, &mw)) return rc;
+  return launch_wide(mx, mw, p, max_split, stream);
 }

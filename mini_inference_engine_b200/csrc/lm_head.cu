@@ -215,15 +215,26 @@ __global__ void __launch_bounds__(kLmThreads, 1)
 }
 
 // keys -> token ids; the keys are cleared for the next call.  `values` (optional) receives the winning
-// bf16 logit's order key (what a vocabulary-sharded caller compares across ranks).
-__global__ void lm_head_finish_kernel(unsigned long long* keys, long long* tokens, int* values, int batch) {
+// bf16 logit's order key (what a vocabulary-sharded caller compares across ranks).  A row whose key was
+// never raised (every CTA gave up on a bounded wait) or decodes to an id outside this call's vocabulary
+// range gets the first id of the range and a status bit, so that whatever consumes the token next (an
+// embedding gather, for one) stays inside its table.
+__global__ void lm_head_finish_kernel(unsigned long long* keys, long long* tokens, int* values, int batch,
+                                      long long vocab_offset, long long vocab, int* status) {
   chain_wait();
   chain_release();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= batch) return;
   const unsigned long long key = keys[b];
-  tokens[b] = (long long)(0xffffffffull - (key & 0xffffffffull));
-  if (values != nullptr) values[b] = (int)(key >> 32);
+  long long token = (long long)(0xffffffffull - (key & 0xffffffffull));
+  int value = (int)(key >> 32);
+  if (key == 0ull || token < vocab_offset || token >= vocab_offset + vocab) {
+    raise_status(status, MIE_STATUS_NO_TOKEN);
+    token = vocab_offset;
+    value = 0;  // below every real logit's key: a vocabulary-sharded caller prefers any other rank's row
+  }
+  tokens[b] = token;
+  if (values != nullptr) values[b] = value;
   keys[b] = 0ull;
 }
 
@@ -326,7 +337,8 @@ extern "C" int mie_lm_head_argmax(const void* x, int64_t ldx, const void* w, int
   }
   if (rc != MIE_OK) return rc;
   MIE_CUDA(launch_chained(lm_head_finish_kernel, dim3((batch + 127) / 128), dim3(128), (size_t)0, stream, p.keys,
-                          reinterpret_cast<long long*>(tokens), values, (int)batch));
+                          reinterpret_cast<long long*>(tokens), values, (int)batch, (long long)vocab_offset,
+                          (long long)vocab, status));
   MIE_LAUNCH_CHECK("lm_head_finish_kernel");
   return MIE_OK;
 }

@@ -6,8 +6,12 @@ sm_100a tcgen05 GEMM and the activation quantiser of ``csrc/fp8_gemm.cu``.
 The contract is the reference's: e4m3 weights ``[N, K]`` with one fp32 inverse
 scale per 128x128 block, bf16/fp16 activations quantised per token and per 128
 columns (``scale = amax / 448``, raw scale kept), every 128-wide K block's dot
-product multiplied by both scales and accumulated in fp32 in increasing K
-order, bias added afterwards.
+product multiplied by both scales and accumulated in fp32, bias added
+afterwards.  By default a shape with too few output tiles for the GPU has the
+K range of a tile cut into parts that are summed separately and then added in
+a fixed order, so the last bit of a row can depend on the batch size;
+``set_batch_invariant(True)`` (or ``MIE_FP8_BATCH_INVARIANT=1``) keeps the
+single increasing-K order of the reference for every row at every batch size.
 
 The reference's ``path="fused" | "split"`` and ``gemm_config`` choose between
 Triton kernels that are bit-identical by construction; here every call runs
@@ -18,6 +22,7 @@ raises.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Any
 
@@ -155,37 +160,68 @@ def quantize_sm89_fp8_activation(input_2d: torch.Tensor) -> tuple[torch.Tensor, 
     return quantized[:, : input_2d.shape[1]], scales[:, : input_2d.shape[0]].t()
 
 
-def _gemm_weight(weight: torch.Tensor) -> torch.Tensor:
-    """The weight as the GEMM needs it: rows contiguous, 16-byte aligned base and row stride.
+# Weights whose layout the GEMM cannot read in place (K not a multiple of 16, unaligned base or rows) are
+# copied once into a padded buffer and found again by (storage address, shape, strides, version counter).
+_PADDED_WEIGHTS: dict[tuple, torch.Tensor] = {}
+_PADDED_WEIGHTS_LIMIT = 256
 
-    Model weights (K a multiple of 16) pass through untouched; odd shapes are
-    copied into a padded buffer on every call.
+# Process-wide default of ``max_split`` for every GEMM launched through this module: 0 lets the library cut
+# the K range of a tile across a thread-block cluster where that is faster; 1 never cuts, which makes every
+# output row the plain increasing-K sum whatever batch it is computed in (the reference's row-independence
+# and path-independence promise, tests/test_sm89_fp8_exact.py).  MIE_FP8_BATCH_INVARIANT=1 selects 1.
+_DEFAULT_MAX_SPLIT = 1 if os.environ.get("MIE_FP8_BATCH_INVARIANT", "0") == "1" else 0
+
+
+def set_batch_invariant(enabled: bool) -> bool:
+    """Make FP8 linear results independent of the batch they are computed in (``max_split = 1``).
+    Returns the previous setting."""
+
+    global _DEFAULT_MAX_SPLIT
+    previous = _DEFAULT_MAX_SPLIT == 1
+    _DEFAULT_MAX_SPLIT = 1 if enabled else 0
+    return previous
+
+
+def _gemm_weight(weight: torch.Tensor) -> tuple[torch.Tensor, bool]:
+    """The weight as the GEMM needs it (rows contiguous, 16-byte aligned base and row stride) and whether
+    a copy was written just now on the current stream.
+
+    Model weights (K a multiple of 16) pass through untouched.  Odd shapes are copied into a padded buffer
+    the first time they are seen; the GEMM that follows that copy must not request weight tiles ahead of
+    its launch-chain wait (``MIE_GEMM_NO_WEIGHT_PREFETCH``), later calls reuse the buffer.
     """
 
     k = weight.shape[1]
     if weight.stride(1) == 1 and weight.stride(0) % 16 == 0 and weight.data_ptr() % 16 == 0:
-        return weight
+        return weight, False
+    key = (weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()), weight._version, weight.device.index)
+    cached = _PADDED_WEIGHTS.get(key)
+    if cached is not None and not torch.cuda.is_current_stream_capturing():
+        return cached, False
     padded = torch.zeros((weight.shape[0], _padded_width(k)), dtype=torch.uint8, device=weight.device)
     padded[:, :k] = weight.contiguous().view(torch.uint8)
-    return padded
+    if not torch.cuda.is_current_stream_capturing():
+        if len(_PADDED_WEIGHTS) >= _PADDED_WEIGHTS_LIMIT:
+            _PADDED_WEIGHTS.clear()
+        _PADDED_WEIGHTS[key] = padded
+    return padded, True
 
 
 def launch_fp8_gemm(quantized: torch.Tensor, scales_kmajor: torch.Tensor, weight: torch.Tensor,
                     weight_scale_inv: torch.Tensor, output: torch.Tensor, m: int, k: int,
-                    status: torch.Tensor | None = None, max_split: int = 0,
-                    trace: torch.Tensor | None = None) -> None:
+                    status: torch.Tensor | None = None, max_split: int | None = None) -> None:
     """``output[m, n] = fp8 block-scaled product``; thin call into ``mie_fp8_gemm``."""
 
     device = output.device
-    w = _gemm_weight(weight)
+    w, fresh_copy = _gemm_weight(weight)
     scales_w = weight_scale_inv if weight_scale_inv.stride(1) == 1 else weight_scale_inv.contiguous()
     word = status if status is not None else _lib.status_word(device)
     _lib.check(_lib.load().mie_fp8_gemm(
         _lib.ptr(quantized), quantized.stride(0), _lib.ptr(scales_kmajor), scales_kmajor.stride(0),
         _lib.ptr(w), w.stride(0), _lib.ptr(scales_w), scales_w.stride(0),
         _lib.ptr(output), output.stride(0), _lib.DTYPE_CODES[output.dtype], m, int(weight.shape[0]), k,
-        int(max_split), _lib.ptr(word), _lib.ptr(trace),
-        _lib.stream_arg(device),
+        int(_DEFAULT_MAX_SPLIT if max_split is None else max_split),
+        _lib.GEMM_NO_WEIGHT_PREFETCH if fresh_copy else 0, _lib.ptr(word), _lib.stream_arg(device),
     ))
 
 
@@ -304,5 +340,5 @@ def install_sm89_fp8_dispatch() -> dict[str, Any]:
 __all__ = [
     "FP8GemmConfig", "MAX_M_BUCKET", "SPLIT_GEMM_CONFIGS", "SPLIT_M_THRESHOLD", "install_sm89_fp8_dispatch",
     "m_bucket", "pretune_sm89_fp8", "pretune_sm89_fp8_shapes", "quantize_sm89_fp8_activation",
-    "select_fp8_path", "sm89_available", "sm89_fp8_linear",
+    "select_fp8_path", "set_batch_invariant", "sm89_available", "sm89_fp8_linear",
 ]
