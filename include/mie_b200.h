@@ -190,7 +190,9 @@ int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mie_view4_t k
  * Limit: mie_decode_scratch_bytes(batch, q_heads, kv_heads, head_dim,
  * max_total_tokens) must not exceed the array (about 64 requests x 4k tokens
  * at 32 query heads); larger batches are rejected with
- * MIE_ERR_INVALID_ARGUMENT and a message, nothing is launched.
+ * MIE_ERR_INVALID_ARGUMENT and a message, nothing is launched.  The check is
+ * made on the sizes alone, so it also turns away large fp32 or odd-head_dim
+ * batches that would have taken the generic kernel and never touched the array.
  *
  * The first call on each device looks the array's device address up (with that
  * device current); make that first call before any stream capture starts.

@@ -9,7 +9,6 @@ elements instead of bit for bit.
 
 from __future__ import annotations
 
-import types
 from typing import Any
 
 import torch
@@ -98,60 +97,135 @@ def _rope_one(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Te
     return out
 
 
-def apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1):
-    """Drop-in for ``transformers.models.qwen3.modeling_qwen3.apply_rotary_pos_emb`` (fused.py:247-262)."""
-
-    supported = (
+def _rope_supported(q, k, cos, sin, unsqueeze_dim) -> bool:
+    return bool(
         unsqueeze_dim == 1 and q.is_cuda and q.dim() == 4 and k.dim() == 4 and cos.dim() == 3
         and q.dtype == k.dtype == cos.dtype == sin.dtype == torch.bfloat16
         and q.stride(-1) == 1 and k.stride(-1) == 1 and cos.stride(-1) == 1 and sin.stride() == cos.stride()
         and q.shape[-1] % 2 == 0 and cos.shape[0] in (1, q.shape[0]) and cos.shape[1] == q.shape[2]
     )
-    if not supported:
+
+
+def apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1):
+    """Drop-in for ``transformers.models.qwen3.modeling_qwen3.apply_rotary_pos_emb`` (fused.py:247-262)."""
+
+    if not _rope_supported(q, k, cos, sin, unsqueeze_dim):
         raise ValueError("apply_rotary_pos_emb: unsupported layout (bf16 CUDA [B, H, T, D] with [B|1, T, D] cos/sin)")
     return _rope_one(q, cos, sin), _rope_one(k, cos, sin)
 
 
 # --- Installation on a Hugging Face Qwen3 model -------------------------------------------------
+#
+# A model is switched over by giving each norm / MLP / decoder-layer module a subclass of its own class
+# whose ``forward`` calls the kernels above (``module.__class__`` is swapped, nothing is copied), and is
+# switched back by restoring the class.  RoPE is a module-level function in Transformers, bound by name in
+# every module that imported it, so it is replaced process-wide in each such module while at least one
+# model is installed.
 
-_ORIGINAL_ROPE: Any = None
-_ROPE_INSTALLS = 0
+_INSTALLED_FLAG = "_minillm_fused_kernels"
 
 
-def _fusable_norm(hidden_states: torch.Tensor) -> bool:
+def _width_ok(hidden_states: torch.Tensor) -> bool:
     width = int(hidden_states.shape[-1])
-    return hidden_states.dtype == torch.bfloat16 and hidden_states.is_cuda and width % 8 == 0 and 128 <= width <= 8192
+    return hidden_states.is_cuda and hidden_states.dtype == torch.bfloat16 and width % 8 == 0 and 128 <= width <= 8192
 
 
-def _norm_forward(self, hidden_states):
-    if not _fusable_norm(hidden_states):
-        return type(self).forward(self, hidden_states)
-    return rms_norm(hidden_states, self.weight, self.variance_epsilon)
+class _FusedNorm:
+    def forward(self, hidden_states):
+        if _width_ok(hidden_states):
+            return rms_norm(hidden_states, self.weight, self.variance_epsilon)
+        return super().forward(hidden_states)
 
 
-def _mlp_forward(self, x):
-    from .merged_projections import project_gate_up
+class _FusedMlp:
+    def forward(self, x):
+        from .merged_projections import project_gate_up
 
-    return self.down_proj(silu_mul(*project_gate_up(self, x)))
+        if not (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16)):
+            return super().forward(x)
+        gate, up = project_gate_up(self, x)
+        return self.down_proj(silu_mul(gate, up))
 
 
-def _decoder_forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_values=None,
-                     use_cache=False, position_embeddings=None, **kwargs):
-    """Qwen3DecoderLayer.forward with the post-attention residual add folded into the next RMSNorm."""
+class _FusedDecoderLayer:
+    """The decoder layer with its post-attention residual add folded into the RMSNorm that follows it."""
 
-    residual = hidden_states
-    hidden_states, _ = self.self_attn(
-        hidden_states=self.input_layernorm(hidden_states), attention_mask=attention_mask,
-        position_ids=position_ids, past_key_values=past_key_values, use_cache=use_cache,
-        position_embeddings=position_embeddings, **kwargs,
-    )
-    norm = self.post_attention_layernorm
-    if _fusable_norm(hidden_states):
-        hidden_states, residual = rms_norm(hidden_states, norm.weight, norm.variance_epsilon, residual=residual)
-    else:
-        residual = residual + hidden_states
-        hidden_states = norm(residual)
-    return residual + self.mlp(hidden_states)
+    def forward(self, hidden_states, attention_mask=None, position_ids=None, past_key_values=None,
+                use_cache=False, position_embeddings=None, **kwargs):
+        attended, _ = self.self_attn(
+            hidden_states=self.input_layernorm(hidden_states), attention_mask=attention_mask,
+            position_ids=position_ids, past_key_values=past_key_values, use_cache=use_cache,
+            position_embeddings=position_embeddings, **kwargs)
+        norm = self.post_attention_layernorm
+        if _width_ok(attended):
+            normed, stream = rms_norm(attended, norm.weight, norm.variance_epsilon, residual=hidden_states)
+        else:
+            stream = hidden_states + attended
+            normed = norm(stream)
+        return stream + self.mlp(normed)
+
+
+_SUBCLASS_CACHE: dict[tuple[type, type], type] = {}
+
+
+def _fused_class(base: type, mixin: type) -> type:
+    key = (base, mixin)
+    if key not in _SUBCLASS_CACHE:
+        _SUBCLASS_CACHE[key] = type(f"Fused{base.__name__}", (mixin, base), {"_mie_plain_class": base})
+    return _SUBCLASS_CACHE[key]
+
+
+def _mixins() -> dict[type, type]:
+    from transformers.models.qwen3 import modeling_qwen3 as hf
+
+    return {hf.Qwen3RMSNorm: _FusedNorm, hf.Qwen3MLP: _FusedMlp, hf.Qwen3DecoderLayer: _FusedDecoderLayer}
+
+
+class _RopeSwitch:
+    """Process-wide, reference-counted replacement of ``apply_rotary_pos_emb`` in every module that binds it
+    by name: Transformers' Qwen3 module and the paged-attention adapter of whichever reference package is
+    imported (its ``engine/kv_cache/qwen3_paged.py`` does ``from ...modeling_qwen3 import apply_rotary_pos_emb``)."""
+
+    def __init__(self) -> None:
+        self.users = 0
+        self.displaced: list[tuple[Any, Any]] = []  # (module, the function it had)
+        self.original: Any = None
+
+    def _targets(self) -> list[Any]:
+        import sys
+
+        from transformers.models.qwen3 import modeling_qwen3 as hf
+
+        adapters = [module for name, module in list(sys.modules.items())
+                    if name.endswith("engine.kv_cache.qwen3_paged") and module is not None
+                    and hasattr(module, "apply_rotary_pos_emb")]
+        return [hf, *adapters]
+
+    def entry(self, q, k, cos, sin, unsqueeze_dim=1):
+        # Calls this library's kernel cannot take (other dtypes or layouts, tensors of other devices: the
+        # patch is process-wide and other models share the symbol) stay with the function that was displaced.
+        if _rope_supported(q, k, cos, sin, unsqueeze_dim):
+            return apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim)
+        return self.original(q, k, cos, sin, unsqueeze_dim)
+
+    def acquire(self) -> None:
+        if self.users == 0:
+            targets = self._targets()
+            self.original = targets[0].apply_rotary_pos_emb
+            for module in targets:
+                self.displaced.append((module, module.apply_rotary_pos_emb))
+                module.apply_rotary_pos_emb = self.entry
+        self.users += 1
+
+    def release(self) -> None:
+        self.users -= 1
+        if self.users == 0:
+            for module, function in self.displaced:
+                module.apply_rotary_pos_emb = function
+            self.displaced.clear()
+
+
+_ROPE = _RopeSwitch()
 
 
 def warm_fused_kernels(model: Any) -> None:
@@ -163,45 +237,35 @@ def warm_fused_kernels(model: Any) -> None:
 
 
 def install_fused_kernels(model: Any) -> bool:
-    """Route a HF Qwen3 model's norms, MLPs, layer adds and RoPE through these kernels (fused.py:350-382)."""
+    """Route a HF Qwen3 model's norms, MLPs, layer adds and RoPE through these kernels
+    (reference: engine/kernels/fused.py:350-382).  False, and nothing changed, without a CUDA device."""
 
-    global _ORIGINAL_ROPE, _ROPE_INSTALLS
-    if getattr(model, "_minillm_fused_kernels", False):
+    if getattr(model, _INSTALLED_FLAG, False):
         return True
     if not fused_kernels_available(next(model.parameters()).device):
         return False
-    from transformers.models.qwen3 import modeling_qwen3
-
-    overrides = {
-        modeling_qwen3.Qwen3RMSNorm: _norm_forward,
-        modeling_qwen3.Qwen3MLP: _mlp_forward,
-        modeling_qwen3.Qwen3DecoderLayer: _decoder_forward,
-    }
+    mixins = _mixins()
     for module in model.modules():
-        for cls, forward in overrides.items():
-            if isinstance(module, cls):
-                module.forward = types.MethodType(forward, module)
-    if _ROPE_INSTALLS == 0:
-        _ORIGINAL_ROPE = modeling_qwen3.apply_rotary_pos_emb
-        modeling_qwen3.apply_rotary_pos_emb = apply_rotary_pos_emb
-    _ROPE_INSTALLS += 1
-    model._minillm_fused_kernels = True
+        if hasattr(type(module), "_mie_plain_class"):
+            continue  # shared with a model that is installed already
+        for base, mixin in mixins.items():
+            if isinstance(module, base):
+                module.__class__ = _fused_class(type(module), mixin)
+                break
+    _ROPE.acquire()
+    setattr(model, _INSTALLED_FLAG, True)
     return True
 
 
 def uninstall_fused_kernels(model: Any) -> None:
-    global _ROPE_INSTALLS
-    if not getattr(model, "_minillm_fused_kernels", False):
+    if not getattr(model, _INSTALLED_FLAG, False):
         return
-    from transformers.models.qwen3 import modeling_qwen3
-
     for module in model.modules():
-        if isinstance(module, (modeling_qwen3.Qwen3RMSNorm, modeling_qwen3.Qwen3MLP, modeling_qwen3.Qwen3DecoderLayer)):
-            module.__dict__.pop("forward", None)
-    _ROPE_INSTALLS -= 1
-    if _ROPE_INSTALLS == 0:
-        modeling_qwen3.apply_rotary_pos_emb = _ORIGINAL_ROPE
-    model._minillm_fused_kernels = False
+        plain = getattr(type(module), "_mie_plain_class", None)
+        if plain is not None:
+            module.__class__ = plain
+    _ROPE.release()
+    setattr(model, _INSTALLED_FLAG, False)
 
 
 __all__ = [

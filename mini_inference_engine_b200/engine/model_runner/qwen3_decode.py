@@ -15,9 +15,14 @@ layer is a dozen launches of this library's kernels:
 
 Tensor parallelism is by heads: rank r of t owns query heads [32r/t, 32(r+1)/t)
 and KV heads [8r/t, 8(r+1)/t) with its own K/V page pool, the merged qkv and
-gate_up projections are column-parallel, o and down are row-parallel and are
-followed by one NCCL all-reduce each; the tied lm_head is vocabulary-sharded
-and greedy sampling exchanges one (value, index) pair per row.
+gate_up projections are column-parallel, o and down are row-parallel.  Their
+partial sums are combined by ``mie_tp_reduce_rms_norm`` (one kernel per rank
+over IPC-mapped peer memory that also does the residual add, the RMSNorm and
+the FP8 quantisation for the next GEMM; ``MIE_TP_EXCHANGE=nccl`` selects a
+plain NCCL all-reduce instead).  The tied lm_head is vocabulary-sharded and
+greedy sampling exchanges one (value, index) pair per row over NCCL.  The
+library is reached through its C-ABI with ``ctypes``; PyTorch owns tensors,
+streams and CUDA graphs only.
 """
 
 from __future__ import annotations
@@ -32,6 +37,11 @@ from ... import _lib
 from ..kernels import sm89_fp8
 from .peer_exchange import PeerExchange
 from ..kv_cache.triton_paged_attention import decode_scratch, launch_decode_attention
+
+
+# A decode work plan carries 64 work counters, one per attention launch that reuses it; deeper models
+# rebuild the plan every 64 layers.
+PLAN_SLOTS = 64
 
 
 @dataclass(frozen=True)
@@ -354,7 +364,8 @@ class Qwen3DecodeRunner:
             launch_decode_attention(queries, attended, self.key_blocks[index], self.value_blocks[index],
                                     block_tables, sequence_lengths, None, scale=scale,
                                     max_total_tokens=batch * self.max_context, scratch=self.scratch,
-                                    split_policy=1, use_plan=index > 0, plan_slot=index, status=self.status,
+                                    split_policy=1, use_plan=index % PLAN_SLOTS != 0,
+                                    plan_slot=index % PLAN_SLOTS, status=self.status,
                                     quantized_out=attn_q)
             _, residual, quantized = self._row_parallel_then_norm(attn_q, layer.o, layer.o_scale, batch, lq * hd,
                                                                   residual, layer.post_norm, quantize=True)

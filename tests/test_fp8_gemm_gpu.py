@@ -111,3 +111,24 @@ def test_rows_are_independent_and_bias_dtype(device, status_clean):
         sm89_fp8.sm89_fp8_linear(xd, w8, w_scale, block_size=[128, 128], path="fast")
     with pytest.raises(RuntimeError, match="no fallback"):
         sm89_fp8.sm89_fp8_linear(xd, w8, w_scale, block_size=[64, 64])
+
+
+@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
+def test_rows_do_not_depend_on_the_batch_in_invariant_mode(name, device, status_clean):
+    """The reference's row-independence promise (tests/test_sm89_fp8_exact.py): with the K range never cut
+    (``set_batch_invariant``), a token's output row is bit-identical whether it is computed alone, in a
+    small batch (narrow kernel) or in a large one (wide kernel, partial last round of tiles included)."""
+
+    x, weight = workloads.gemm_case(name, 1000, seed=3)
+    w8, w_scale = hot_path.quantize_weight(weight)
+    xd, w8, w_scale = x.to(device), w8.to(device), w_scale.to(device)
+    previous = sm89_fp8.set_batch_invariant(True)
+    try:
+        full = sm89_fp8.sm89_fp8_linear(xd, w8, w_scale, block_size=[128, 128])
+        for rows in (1, 7, 129):
+            part = sm89_fp8.sm89_fp8_linear(xd[:rows], w8, w_scale, block_size=[128, 128])
+            assert torch.equal(part, full[:rows]), (name, rows)
+        single = sm89_fp8.sm89_fp8_linear(xd[999:1000], w8, w_scale, block_size=[128, 128])
+        assert torch.equal(single, full[999:1000])
+    finally:
+        sm89_fp8.set_batch_invariant(previous)

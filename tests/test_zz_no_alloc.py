@@ -34,7 +34,8 @@ def _static_call(case, out, *, max_total_tokens, split_policy=1):
 def test_static_scratch_entry_matches_the_regular_entry_twice_in_a_row(device):
     assert _lib.load().mie_decode_builtin_scratch_bytes() == 16 << 20
     # Two different batches back to back: the second call finds the first call's plan and partials in the
-    # shared array and must not be affected by them.
+    # shared array and must not be affected by them.  Both entry points build the same plan and run the same
+    # kernels, only the scratch address differs, so the outputs are compared bit for bit.
     for lengths, seed in (((17, 128, 513, 2048), 0), ((4096, 33, 1000, 16, 700, 2500), 5)):
         case = workloads.decode_case(lengths, seed=seed, num_pages=640).to(device)
         total = sum(lengths)
@@ -45,9 +46,26 @@ def test_static_scratch_entry_matches_the_regular_entry_twice_in_a_row(device):
         _lib.check(_static_call(case, got, max_total_tokens=total))
         torch.cuda.synchronize()
         assert torch.isfinite(got.float()).all()
-        assert (got.float() - expected.float()).abs().max().item() <= ATOL
+        assert torch.equal(got, expected)
     word = _lib.status_word(device)
     assert int(word.item()) == 0
+
+
+def test_static_scratch_entry_matches_the_reference_golden_output(golden, device):
+    """Not a self-comparison: BASELINE configuration 0 against the output the reference's torch path gave."""
+
+    meta = golden("decode_cfg0")
+    case = workloads.decode_case(meta["lengths"], seed=meta["seed"], num_pages=meta["num_pages"], page=meta["page"],
+                                 q_heads=meta["q_heads"], kv_heads=meta["kv_heads"],
+                                 head_dim=meta["head_dim"]).to(device)
+    for _ in range(2):
+        got = torch.full_like(case.query, float("nan"))
+        _lib.check(_static_call(case, got, max_total_tokens=sum(meta["lengths"])))
+        torch.cuda.synchronize()
+        result = got.transpose(1, 2).cpu()
+        assert result.shape == meta["output"].shape
+        assert (result.float() - meta["output"].float()).abs().max().item() <= ATOL
+    assert int(_lib.status_word(device).item()) == 0
 
 
 def test_static_scratch_entry_rejects_batches_beyond_its_array(device):
