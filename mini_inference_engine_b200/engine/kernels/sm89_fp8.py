@@ -161,9 +161,10 @@ def quantize_sm89_fp8_activation(input_2d: torch.Tensor) -> tuple[torch.Tensor, 
 
 
 # Weights whose layout the GEMM cannot read in place (K not a multiple of 16, unaligned base or rows) are
-# copied once into a padded buffer and found again by (storage address, shape, strides, version counter).
-_PADDED_WEIGHTS: dict[tuple, torch.Tensor] = {}
-_PADDED_WEIGHTS_LIMIT = 256
+# copied into a padded buffer.  The copy is remembered ON the tensor object that was passed (an attribute,
+# together with the tensor's version counter), so a module's parameter is copied once, while a temporary is
+# copied on every call; nothing is keyed by address, which an allocator may hand to another tensor.
+_PADDED_ATTR = "_mie_padded_weight"
 
 # Process-wide default of ``max_split`` for every GEMM launched through this module: 0 lets the library cut
 # the K range of a tile across a thread-block cluster where that is faster; 1 never cuts, which makes every
@@ -194,16 +195,17 @@ def _gemm_weight(weight: torch.Tensor) -> tuple[torch.Tensor, bool]:
     k = weight.shape[1]
     if weight.stride(1) == 1 and weight.stride(0) % 16 == 0 and weight.data_ptr() % 16 == 0:
         return weight, False
-    key = (weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()), weight._version, weight.device.index)
-    cached = _PADDED_WEIGHTS.get(key)
-    if cached is not None and not torch.cuda.is_current_stream_capturing():
-        return cached, False
+    capturing = torch.cuda.is_current_stream_capturing()
+    cached = getattr(weight, _PADDED_ATTR, None)
+    if cached is not None and cached[1] == weight._version and not capturing:
+        return cached[0], False
     padded = torch.zeros((weight.shape[0], _padded_width(k)), dtype=torch.uint8, device=weight.device)
     padded[:, :k] = weight.contiguous().view(torch.uint8)
-    if not torch.cuda.is_current_stream_capturing():
-        if len(_PADDED_WEIGHTS) >= _PADDED_WEIGHTS_LIMIT:
-            _PADDED_WEIGHTS.clear()
-        _PADDED_WEIGHTS[key] = padded
+    if not capturing:
+        try:
+            setattr(weight, _PADDED_ATTR, (padded, weight._version))
+        except (AttributeError, RuntimeError):
+            pass
     return padded, True
 
 
