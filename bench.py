@@ -262,7 +262,7 @@ def leave_together(runner, device) -> None:
     communicator's destructor (destroying a communicator that graphs had captured blocked one earlier run;
     with the graphs gone and NVLS off nothing is bound to a peer when the process exits)."""
 
-    runner._graphs.clear()
+    runner.release_graphs()
     torch.cuda.synchronize(device)
     torch.distributed.barrier()
     torch.cuda.synchronize(device)
@@ -371,7 +371,7 @@ def main() -> None:
     buffers.block_tables.copy_(tables.to(device))
     buffers.sequence_lengths.copy_((contexts + 1).to(torch.int32).to(device))
     for _ in range(warmup):
-        runner.replay(concurrency)
+        runner.replay(concurrency, advance=True)
     barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -380,7 +380,7 @@ def main() -> None:
     torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` list only the timed launches
     start.record()
     for _ in range(steps):
-        runner.replay(concurrency)
+        runner.replay(concurrency, advance=True)
     end.record()
     barrier()
     torch.cuda.profiler.stop()

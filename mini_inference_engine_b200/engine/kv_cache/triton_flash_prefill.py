@@ -43,19 +43,32 @@ def triton_flash_prefill_attention(
         raise ValueError("the last (head_dim) dimension must be contiguous")
     if query.dtype not in (torch.bfloat16, torch.float16) or key_blocks.dtype != query.dtype:
         raise ValueError("flash prefill supports bf16/fp16 queries and pages of the same dtype")
-    requests = int(cu_seqlens.shape[0]) - 1
     out = torch.empty_like(query)
-    if tokens == 0 or requests == 0:
-        return out
+    launch_flash_prefill(query, out, key_blocks, value_blocks, block_tables, cu_seqlens, kv_lens,
+                         max_query_len=max_query_len, scale=scale)
+    return out
+
+
+def launch_flash_prefill(query, out, key_blocks, value_blocks, block_tables, cu_seqlens, kv_lens, *,
+                         max_query_len: int, scale: float, status: torch.Tensor | None = None) -> None:
+    """Thin call into ``mie_flash_prefill_attention`` writing into ``out`` (``[tokens, heads, dim]``, same
+    dtype as the query, last dimension contiguous).  Rows of ``query`` that no ``cu_seqlens`` range covers
+    are left untouched in ``out``."""
+
+    tokens, heads, head_dim = (int(x) for x in query.shape)
+    num_blocks, kv_heads, page, _ = (int(x) for x in key_blocks.shape)
+    requests = int(cu_seqlens.shape[0]) - 1
+    if tokens == 0 or requests <= 0:
+        return
     device = query.device
+    word = status if status is not None else _lib.status_word(device)
     _lib.check(_lib.load().mie_flash_prefill_attention(
         _lib.ptr(query), query.stride(0), query.stride(1), tokens, _lib.ptr(out), out.stride(0), out.stride(1),
         _lib.view4_arg(key_blocks), _lib.view4_arg(value_blocks), _lib.index_arg(block_tables),
         _lib.index_arg(cu_seqlens), _lib.index_arg(kv_lens), requests, int(max_query_len), heads, kv_heads,
         head_dim, page, num_blocks, int(block_tables.shape[1]), _lib.DTYPE_CODES[query.dtype], float(scale),
-        _lib.ptr(_lib.status_word(device)), _lib.stream_arg(device),
+        _lib.ptr(word), _lib.stream_arg(device),
     ))
-    return out
 
 
-__all__ = ["triton_flash_prefill_attention"]
+__all__ = ["triton_flash_prefill_attention"]  # launch_flash_prefill is this package's own lower-level entry

@@ -1,7 +1,13 @@
 """The CUDA-graph decode step of a small Qwen3-shaped FP8 model against the CPU oracle.
 
-Short configuration (2 layers, width 512, 4 query / 2 KV heads of 128, vocab 2048):
-greedy tokens must be identical; the final hidden rows agree within bf16 tolerance.
+Short configuration (2 layers, width 512, 4 query / 2 KV heads of 128, vocab 2048).
+
+* ``test_generation_tokens_equal_the_oracle``: whole generations (packed prefill + graph decode steps) on
+  seeds for which the oracle's own top-2 logit gap is at least 4.5 % of its top logit at every step; the
+  tokens are compared with ``==`` - the bit-exact bar for greedy tokens of the short configurations.
+* ``test_tokens_within_the_noise_band_on_random_state``: decode steps from an arbitrary random cache, where
+  the oracle's own logits can sit a few bf16 ulps apart; there equality is demanded wherever the oracle's
+  margin exceeds the bf16 noise of two forwards, and a near-maximal token inside that band.
 """
 
 from __future__ import annotations
@@ -33,7 +39,7 @@ def _cpu_weights(weights):
 
 
 @pytest.mark.parametrize("use_graph", [False, True])
-def test_greedy_tokens_match_the_oracle(use_graph, device):
+def test_tokens_within_the_noise_band_on_random_state(use_graph, device):
     torch.manual_seed(0)
     weights = Qwen3Weights(SHAPE, device, seed=1)
     lengths = torch.tensor([5, 33, 130], dtype=torch.int32)
@@ -60,7 +66,7 @@ def test_greedy_tokens_match_the_oracle(use_graph, device):
             head_dim=SHAPE.head_dim, eps=SHAPE.rms_eps, theta=SHAPE.rope_theta, return_hidden=True)
         if use_graph:
             buffers.input_ids.copy_(ids.to(device))  # keep both sides on the oracle's token stream
-            runner.replay(3)
+            runner.replay(3, advance=True)
             got, logits = buffers.output_tokens.cpu(), None
         else:
             got, logits = runner.decode_forward(ids.to(device), current.to(device), tables_dev, return_logits=True)
@@ -99,63 +105,29 @@ def test_launch_count_is_reported(device):
     assert runner.launches_per_step == 2 * 10 + 2 + 2
 
 
-def _check_tokens(got, expected, logits_ref, where):
-    reference_logits = logits_ref.float()
-    top2 = reference_logits.topk(2, dim=-1).values
-    noise = top2[:, 0].abs() * 2.0 ** -6
-    decided = 0
-    for row in range(got.shape[0]):
-        if top2[row, 0] - top2[row, 1] > noise[row]:
-            assert got[row] == expected[row], (where, row, got, expected)
-            decided += 1
-        else:
-            assert reference_logits[row, got[row]] >= top2[row, 0] - noise[row], (where, row, got, expected)
-    return decided
-
-
-def test_packed_prefill_then_generation_matches_the_oracle(device):
+def test_generation_tokens_equal_the_oracle(device):
     """Short form of BASELINE configuration 3: requests arrive together, one packed whole-prompt prefill, then
-    greedy decode steps; tokens are compared with the CPU oracle's at every step."""
+    greedy decode steps (eager, then replayed from the bucket's graph that feeds its own tokens back); every
+    token of every request equals the CPU oracle's."""
 
-    torch.manual_seed(0)
-    weights = Qwen3Weights(SHAPE, device, seed=2)
-    cpu = _cpu_weights(weights)
-    generator = torch.Generator().manual_seed(3)
+    from oracle_generation import oracle_generate
+
+    cpu = Qwen3Weights(SHAPE, torch.device("cpu"), seed=31)  # drawn on the CPU: the same model on every host
+    weights = cpu.to(device)
+    generator = torch.Generator().manual_seed(1)
+    new_tokens = 12
     prompts = [torch.randint(0, SHAPE.vocab, (n,), generator=generator).tolist() for n in (37, 5, 130)]
-    new_tokens = 4
+    expected = []
+    for prompt in prompts:
+        tokens, margin = oracle_generate(cpu, SHAPE, prompt, new_tokens)
+        assert margin >= 0.045, f"the oracle itself is not decisive: margin {margin:.4f}"
+        expected.append(tokens)
     runner = Qwen3DecodeRunner(weights, num_pages=32, max_batch=3, max_context=256)
-    for use_graph in (False, True):
+    for use_graph in (False, True, True):  # the third run reuses the captured bucket
         runner.key_blocks.zero_()
         runner.value_blocks.zero_()
-        got = runner.generate(prompts, new_tokens, use_graph=use_graph)
-        # Oracle: same page assignment as generate() (in order from the start of the pool).
-        lengths = [len(p) for p in prompts]
-        needed = [-(-(n + new_tokens) // 16) for n in lengths]
-        tables = torch.full((3, max(needed)), -1, dtype=torch.int32)
-        cursor = 0
-        for row, pages in enumerate(needed):
-            tables[row, :pages] = torch.arange(cursor, cursor + pages, dtype=torch.int32)
-            cursor += pages
-        key_cpu = torch.zeros(SHAPE.layers, 32, SHAPE.kv_heads, 16, 128, dtype=torch.bfloat16)
-        value_cpu = torch.zeros_like(key_cpu)
-        flat = torch.tensor([t for p in prompts for t in p])
-        tok2seq = torch.cat([torch.full((n,), r, dtype=torch.int32) for r, n in enumerate(lengths)])
-        tokpos = torch.cat([torch.arange(n, dtype=torch.int32) for n in lengths])
-        cu = torch.zeros(4, dtype=torch.int32)
-        cu[1:] = torch.tensor(lengths).cumsum(0)
-        kv_lens = torch.tensor(lengths, dtype=torch.int32)
-        kwargs = dict(q_heads=SHAPE.q_heads, kv_heads=SHAPE.kv_heads, head_dim=SHAPE.head_dim, eps=SHAPE.rms_eps,
-                      theta=SHAPE.rope_theta, return_hidden=True)
-        expected, _, logits = qwen3_model.prefill_step(cpu, key_cpu, value_cpu, flat, tok2seq, tokpos, tables, cu,
-                                                       kv_lens, **kwargs)
-        decided = _check_tokens(torch.tensor([row[0] for row in got]), expected, logits, "prefill")
-        ids, current = expected, kv_lens.clone()
-        for step in range(1, new_tokens):
-            current = current + 1
-            if [row[step - 1] for row in got] != ids.tolist():
-                break  # a tie was broken differently: the streams legitimately part ways here
-            expected, _, logits = qwen3_model.decode_step(cpu, key_cpu, value_cpu, ids, current, tables, **kwargs)
-            decided += _check_tokens(torch.tensor([row[step] for row in got]), expected, logits, f"decode {step}")
-            ids = expected
-        assert decided >= 6
-        assert all(len(row) == new_tokens for row in got)
+        assert runner.generate(prompts, new_tokens, use_graph=use_graph) == expected
+    assert int(runner.status.item()) == 0
+    assert ("decode", 3, True) in runner._graphs
+
+
