@@ -49,6 +49,8 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--workload", default="config4", choices=["config4", "config3"],
                         help="config4: ragged decode sweep point (the headline); config3: 8 x (2048 prompt + 128 new)")
+    parser.add_argument("--breakdown", action="store_true",
+                        help="instead of the benchmark: CUDA-event time per kernel class of the eager decode step")
     parser.add_argument("--watchdog", type=int, default=900,
                         help="seconds after which every rank dumps its Python stacks and exits (0 = off)")
     return parser.parse_args()
@@ -256,6 +258,69 @@ def run_config3(args, shape, device, rank, world, group) -> None:
         leave_together(runner, device)
 
 
+def run_breakdown(runner, buffers, steps: int, device, rank: int, world: int, concurrency: int) -> None:
+    """CUDA-event time per kernel class of the decode step, run eagerly (no graph) with the stream kept busy
+    ahead of the launches so that the intervals hold device time, not launch gaps.  Under tensor parallelism
+    the exchange kernels wait for their peers, so their time includes the skew between ranks; every rank
+    measures, rank 0 prints its own figures."""
+
+    from mini_inference_engine_b200.engine.model_runner import qwen3_decode
+
+    spans: dict[str, list] = {}
+
+    def timed(name_of, fn):
+        def wrapper(*args, **kwargs):
+            name = name_of(*args, **kwargs)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            out = fn(*args, **kwargs)
+            e1.record()
+            spans.setdefault(name, []).append((e0, e1))
+            return out
+        return wrapper
+
+    layer0 = runner.weights.layers[0]
+    shapes = {tuple(layer0.qkv.shape): "gemm qkv", tuple(layer0.o.shape): "gemm o",
+              tuple(layer0.gate_up.shape): "gemm gate_up", tuple(layer0.down.shape): "gemm down"}
+    runner._gemm = timed(lambda q, w, *a, **k: shapes.get(tuple(w.shape), "gemm other"), runner._gemm)
+    runner._norm = timed(lambda *a, **k: "add + rms_norm (+quant)", runner._norm)
+    runner._qkv_post = timed(lambda *a, **k: "q/k norm + rope + kv write", runner._qkv_post)
+    runner._silu_mul_quantized = timed(lambda *a, **k: "silu*up + quant", runner._silu_mul_quantized)
+    runner.greedy_tokens = timed(lambda *a, **k: "lm_head + greedy sampling", runner.greedy_tokens)
+    qwen3_decode.launch_decode_attention = timed(lambda *a, **k: "decode attention (plan + decode + merge)",
+                                                 qwen3_decode.launch_decode_attention)
+    if runner.exchange is not None:
+        runner.exchange.reduce_norm = timed(lambda *a, **k: "peer exchange + add + rms_norm + quant",
+                                            runner.exchange.reduce_norm)
+    totals = []
+    for step in range(steps + 1):
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+        spans.clear()
+        torch.cuda._sleep(40_000_000)  # ~20 ms of device time: the host queues the whole step behind it
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        runner.decode_forward(buffers.input_ids, buffers.sequence_lengths, buffers.block_tables)
+        s1.record()
+        torch.cuda.synchronize(device)
+        if step:  # the first pass warms up
+            totals.append((s0.elapsed_time(s1), {n: [a.elapsed_time(b) for a, b in v] for n, v in spans.items()}))
+    runner.check_status()
+    if rank == 0:
+        classes = {}
+        for name in totals[0][1]:
+            per_call = [t for _, per in totals for t in per[name]]
+            classes[name] = {"calls_per_step": len(totals[0][1][name]),
+                             "us_per_call": sum(per_call) / len(per_call) * 1e3,
+                             "ms_per_step": sum(per_call) / len(totals)}
+        step_ms = sum(t for t, _ in totals) / len(totals)
+        emit({"breakdown": "eager decode step, CUDA events per kernel class", "n_gpus": world,
+              "concurrency": concurrency, "eager_step_ms": step_ms,
+              "sum_of_classes_ms": sum(c["ms_per_step"] for c in classes.values()),
+              "classes": dict(sorted(classes.items(), key=lambda kv: -kv[1]["ms_per_step"]))})
+
+
 def leave_together(runner, device) -> None:
     """End a multi-rank run: drop the captured graphs (they hold NCCL kernels and peer-memory pointers), wait
     for the device and for every rank, unmap the peers' exchange blocks, then exit without running the
@@ -370,6 +435,11 @@ def main() -> None:
     buffers.input_ids.copy_(ids0.to(device))
     buffers.block_tables.copy_(tables.to(device))
     buffers.sequence_lengths.copy_((contexts + 1).to(torch.int32).to(device))
+    if args.breakdown:
+        run_breakdown(runner, buffers, max(1, min(steps, 5)), device, rank, world, concurrency)
+        if world > 1:
+            leave_together(runner, device)
+        return
     for _ in range(warmup):
         runner.replay(concurrency, advance=True)
     barrier()
@@ -480,8 +550,11 @@ def main() -> None:
     if rank == 0 and not args.no_cpu_baseline:
         use_all_host_cores()
         try:
-            cpu_all = cpu_decode_baseline(layer_source=weights.layers[0], embedding=weights.embedding,
-                                          final_norm=weights.final_norm)
+            if world == 1:
+                cpu_all = cpu_decode_baseline(layer_source=weights.layers[0], embedding=weights.embedding,
+                                              final_norm=weights.final_norm)
+            else:  # this rank holds a shard: the baseline runs the unsharded layer, drawn on the CPU
+                cpu_all = cpu_decode_baseline()
             cpu = {k: cpu_all[k] for k in ("value", "unit", "cores", "kind", "sample")}
         except Exception as error:  # the baseline is reported, never required
             cpu = {"value": None, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",

@@ -212,6 +212,50 @@ int mie_paged_decode_attention_static(mie_view4_t query, mie_view4_t out, mie_vi
                                       void* stream);
 
 /* ------------------------------------------------------------------------
+ * FP8 (e4m3) KV cache: decode attention and the writer that fills it
+ * ---------------------------------------------------------------------- */
+
+/*
+ * The reference keeps K/V in the model dtype; it only names an FP8 cache as the
+ * next step for its HBM-bound decode (docs/phase_notes/roofline.md:76), so these
+ * two entries extend mie_paged_decode_attention / mie_qkv_norm_rope_write and
+ * have no reference implementation to be pinned against.
+ *
+ * Layout (page size 16, head_dim 128): kv_pool [num_blocks][kv_heads][2][16][128]
+ * bytes - per page and KV head the 16 K rows then the 16 V rows, e4m3 - with a
+ * page stride of page_stride_bytes (>= kv_heads * 4096, so one layer can be a
+ * slice of a bigger pool), 1 KiB aligned; kv_scales [num_blocks][kv_heads][2][16]
+ * fp32, one scale per (token, KV head) for K and for V: scale = amax / 448 of
+ * the row, row / max(scale, 1e-12) rounded to e4m3 (mie_fp8_quantize's rule).
+ * 2,112 bytes per token and layer at 8 KV heads instead of 4,096.
+ *
+ * mie_paged_decode_attention_kv8 is mie_paged_decode_attention on that pool:
+ * same query / output tensors (bf16 or fp16), metadata, split policy, scratch,
+ * plans and optional e4m3 output for o_proj.  Scores are (q . k8) * k_scale in
+ * fp32, rounded to the query dtype like the bf16 path; the V scale of a token is
+ * folded into its probability before P . V.
+ */
+int mie_paged_decode_attention_kv8(mie_view4_t query, mie_view4_t out, const void* kv_pool,
+                                   int64_t page_stride_bytes, const float* kv_scales, mie_index_t block_tables,
+                                   mie_index_t sequence_lengths, mie_index_t query_positions /* ptr may be NULL */,
+                                   int32_t batch, int32_t q_heads, int32_t kv_heads, int32_t num_blocks,
+                                   int32_t table_width, int32_t dtype, float scale, int32_t split_policy,
+                                   void* scratch, int64_t scratch_bytes, int32_t plan_only, int32_t use_plan,
+                                   int32_t plan_slot, void* out_q8 /* may be NULL */, int64_t ldq8,
+                                   float* out_scales, int32_t out_scale_ld, int32_t* status, void* stream);
+
+/*
+ * mie_qkv_norm_rope_write with the K/V rows quantised into the FP8 pool above
+ * instead of copied to bf16 pages (q rows, norms and RoPE are unchanged).
+ */
+int mie_qkv_norm_rope_write_kv8(const void* qkv, int64_t ld, const void* q_weight, const void* k_weight,
+                                const void* cos_sin, int32_t max_pos, mie_index_t positions,
+                                mie_index_t token_to_sequence, mie_index_t block_tables, void* q_out, void* kv_pool,
+                                int64_t page_stride_bytes, float* kv_scales, int32_t tokens, int32_t q_heads,
+                                int32_t kv_heads, int32_t num_blocks, int32_t table_rows, int32_t table_width,
+                                float eps, int32_t* status, void* stream);
+
+/* ------------------------------------------------------------------------
  * Chunked-prefill attention
  * ---------------------------------------------------------------------- */
 

@@ -59,21 +59,35 @@ def decode(args, device) -> dict:
     pages = sum(-(-int(n) // workloads.PAGE) for n in lengths) + 8
     tables = workloads.random_block_tables(lengths, num_pages=pages, seed=1).to(device)
     kv_heads, q_heads = workloads.KV_HEADS // args.tp, workloads.Q_HEADS // args.tp
-    key_blocks = torch.randn(pages, kv_heads, workloads.PAGE, 128, device=device).to(torch.bfloat16)
-    value_blocks = torch.randn(pages, kv_heads, workloads.PAGE, 128, device=device).to(torch.bfloat16)
     query = torch.randn(args.concurrency, q_heads, 1, 128, device=device).to(torch.bfloat16)
     out = torch.empty_like(query)
     lens = lengths.to(torch.int32).to(device)
     scratch = decode_scratch(args.concurrency, q_heads, kv_heads, 128, total, device)
+    if args.kv_dtype == "fp8":
+        from mini_inference_engine_b200.engine.kv_cache.fp8_kv import Fp8KvPool, launch_decode_attention_kv8
 
-    def run():
-        launch_decode_attention(query, out, key_blocks, value_blocks, tables, lens, None, scale=128 ** -0.5,
-                                max_total_tokens=total, scratch=scratch, split_policy=args.split_policy)
+        pool = Fp8KvPool(1, pages, kv_heads, device)
+        pool.data.random_(0, 256).bitwise_and_(0xBF)  # random e4m3 bytes without NaN patterns
+        pool.scales.uniform_(0.004, 0.012)
+        bytes_per_token = pool.bytes_per_token()
+
+        def run():
+            launch_decode_attention_kv8(query, out, pool.data[0], pool.scales[0], tables, lens, None,
+                                        scale=128 ** -0.5, scratch=scratch, split_policy=args.split_policy)
+    else:
+        key_blocks = torch.randn(pages, kv_heads, workloads.PAGE, 128, device=device).to(torch.bfloat16)
+        value_blocks = torch.randn(pages, kv_heads, workloads.PAGE, 128, device=device).to(torch.bfloat16)
+        bytes_per_token = 2 * kv_heads * 128 * 2
+
+        def run():
+            launch_decode_attention(query, out, key_blocks, value_blocks, tables, lens, None, scale=128 ** -0.5,
+                                    max_total_tokens=total, scratch=scratch, split_policy=args.split_policy)
 
     ms = _time(run, args.repeats, device)
-    algorithmic = total * 2 * kv_heads * 128 * 2 + 2 * query.numel() * 2
-    return {"kernel": "paged decode attention (plan + decode)", "concurrency": args.concurrency,
-            "total_context_tokens": total, "us_per_launch": ms * 1e3, "algorithmic_bytes": algorithmic,
+    algorithmic = total * bytes_per_token + 2 * query.numel() * 2
+    return {"kernel": f"paged decode attention (plan + decode + merge), {args.kv_dtype} KV",
+            "concurrency": args.concurrency, "total_context_tokens": total, "us_per_launch": ms * 1e3,
+            "kv_bytes_per_token": bytes_per_token, "algorithmic_bytes": algorithmic,
             "gb_per_s": algorithmic / ms / 1e6}
 
 
@@ -146,6 +160,7 @@ def main() -> None:
     p.add_argument("--concurrency", type=int, default=64)
     p.add_argument("--tp", type=int, default=1)
     p.add_argument("--split-policy", type=int, default=1)
+    p.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"])
     p = sub.add_parser("gemm")
     p.add_argument("--shape", default="qkv", choices=list(workloads.GEMM_SHAPES))
     p.add_argument("--rows", type=int, default=256)

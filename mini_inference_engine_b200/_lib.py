@@ -82,6 +82,15 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
                                                   c_int32, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
                                                   c_float, c_int32, c_int64, c_void_p, c_int64, c_int32, c_int32,
                                                   c_int32, c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_void_p]),
+    "mie_paged_decode_attention_kv8": (ctypes.c_int, [View4T, View4T, c_void_p, c_int64, c_void_p, IndexT, IndexT,
+                                                      IndexT, c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,
+                                                      c_float, c_int32, c_void_p, c_int64, c_int32, c_int32,
+                                                      c_int32, c_void_p, c_int64, c_void_p, c_int32, c_void_p,
+                                                      c_void_p]),
+    "mie_qkv_norm_rope_write_kv8": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int32, IndexT,
+                                                   IndexT, IndexT, c_void_p, c_void_p, c_int64, c_void_p, c_int32,
+                                                   c_int32, c_int32, c_int32, c_int32, c_int32, c_float, c_void_p,
+                                                   c_void_p]),
     "mie_decode_builtin_scratch_bytes": (c_int64, []),
     "mie_paged_decode_attention_static": (ctypes.c_int, [View4T, View4T, View4T, View4T, IndexT, IndexT, IndexT,
                                                          c_int32, c_int32, c_int32, c_int32, c_int32, c_int32,

@@ -450,6 +450,337 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   }
 }
 
+// ---------------------------------------------------------------------------
+// Main kernel over an e4m3 K/V pool (one fp32 scale per token and KV head)
+// ---------------------------------------------------------------------------
+// Pool layout [pages][kv_heads][2 = K, V][16 tokens][128 bytes] with scales [pages][kv_heads][2][16] fp32,
+// so one page of one head is a single 4 KiB TMA box (K rows then V rows) plus one 128-byte bulk copy of
+// its 32 scales: two copy instructions per 16 tokens instead of four.  Same work plan, same persistent
+// warps and the same outputs (final rows, split-KV partials, e4m3 rows for o_proj) as decode_kernel.
+//
+// Arithmetic.  The e4m3 bytes are widened to fp16 in registers (exact) and both products run as fp16
+// mma.sync with fp32 accumulation.  S = (q . k8) * k_scale[token]: the scale is applied to the fp32 dot
+// product.  O += P . (v8 * v_scale): the scale of token j is folded into its probability, normalised by the
+// largest V scale of the 16-token tile and lifted by 2^10 so that small probabilities stay normal fp16
+// numbers; the tile's product is then added into the running output with the inverse factor.
+// Fragment trick: ldmatrix hands a thread 4 consecutive bytes of a row; for Q.K^T they are taken as the
+// k-slots (2t, 2t+1 | 2t+8, 2t+9) of the MMA, with the query fragment read in the same permuted order
+// (a dot product does not care), and for P.V the transposed load yields two tokens x two adjacent
+// dimensions, which a byte permute splits into the B fragments of an "even dimensions" and an "odd
+// dimensions" n-tile.
+constexpr int kStages8 = 4;
+constexpr int kTile8Bytes = kTileTokens * kHeadDim;    // 2 KiB of K or of V
+constexpr int kStage8Bytes = 2 * kTile8Bytes + 1024;  // K + V + (128 bytes of scales, padded to the 1 KiB grid)
+
+__device__ __forceinline__ void bulk_load_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar,
+                                               uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+      :
+      : "r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+
+// Two e4m3 values (low 16 bits of `pair`) -> two fp16 values, exact.
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t pair) {
+  uint32_t out;
+  const unsigned short lo = (unsigned short)(pair & 0xffffu);
+  asm volatile("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(out) : "h"(lo));
+  return out;
+}
+
+template <typename T>
+__device__ __forceinline__ uint32_t act_pair_to_f16x2(uint32_t raw);
+template <>
+__device__ __forceinline__ uint32_t act_pair_to_f16x2<__half>(uint32_t raw) {
+  return raw;
+}
+template <>
+__device__ __forceinline__ uint32_t act_pair_to_f16x2<__nv_bfloat16>(uint32_t raw) {
+  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&raw);
+  const float2 f = __bfloat1622float2(v);
+  return Mma16816<__half>::pack(f.x, f.y);
+}
+
+struct Kv8Params {
+  const float* kv_scales;  // [num_blocks][kv_heads][2][16]
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32, 1)
+    decode_kv8_kernel(const __grid_constant__ CUtensorMap kvmap, const DecodeParams p, const Kv8Params kv) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(align_up((long long)reinterpret_cast<uintptr_t>(smem_raw), 1024));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* stages = smem + (size_t)warp * kStages8 * kStage8Bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * kStages8 * kStage8Bytes) + warp * kStages8;
+  int* pids = reinterpret_cast<int*>(smem + (size_t)kWarps * kStages8 * kStage8Bytes + kWarps * kStages8 * 8) +
+              warp * kPidBatch;
+
+  if (lane == 0) {
+    for (int s = 0; s < kStages8; ++s) mbar_init(&bars[s], 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&kvmap);
+  }
+  __syncthreads();
+  chain_wait();
+  chain_release();
+
+  const int g = lane >> 2, t = lane & 3;
+  const int chunk = p.sc.header[0];
+  const int total_items = p.sc.header[2];
+  int* counter = p.sc.header + kCounterBase + p.counter_slot;
+  const long long capacity_tokens = (long long)p.table_width * p.block_size;
+  uint32_t parity = 0;
+  const uint64_t stream_policy = l2_evict_first_policy();  // K/V pages are read once per step
+
+  // ldmatrix lane geometry: lane i addresses row (i & 7) of matrix (i >> 3); matrices 0/1 are tokens
+  // 0-7 / 8-15 of one 16-byte column chunk, matrices 2/3 the same tokens of the next chunk.
+  const int m_tok = (lane & 7) + ((lane >> 3) & 1) * 8, m_sel = (lane >> 4) & 1;
+  const uint32_t m_row = m_tok * 128, m_key = m_tok & 7;
+
+  while (true) {
+    int item = 0;
+    if (lane == 0) item = atomicAdd(counter, 1);
+    item = __shfl_sync(0xffffffffu, item, 0);
+    if (item >= total_items) break;
+    const int sci = item / p.kv_heads, h = item % p.kv_heads;
+    const int b = p.sc.item_seq[sci], ck = p.sc.item_chunk[sci];
+    const long long rl = read_length(p.lengths, p.positions, b, capacity_tokens, nullptr);
+    const int nchunks = p.sc.offsets[b + 1] - p.sc.offsets[b];
+    const long long t_begin = (long long)ck * chunk;
+    const long long t_end = rl < t_begin + chunk ? rl : t_begin + chunk;
+    const int ntiles = (int)((t_end - t_begin + kTileTokens - 1) / kTileTokens);
+
+    // Query fragments in the permuted k order: step c covers dims [16c, 16c + 16), this lane holds dims
+    // 16c + 4t .. 16c + 4t + 3 of head g.  Rows g >= group are zero.
+    uint32_t qa[8][2];
+    {
+      const bool real = g < p.group;
+      const T* qrow = reinterpret_cast<const T*>(p.q.ptr) + (long long)b * p.q.s[0] +
+                      (long long)(h * p.group + (real ? g : 0)) * p.q.s[1];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(qrow + c * 16 + 4 * t);
+        qa[c][0] = real ? act_pair_to_f16x2<T>(raw.x) : 0u;
+        qa[c][1] = real ? act_pair_to_f16x2<T>(raw.y) : 0u;
+      }
+    }
+
+    float m = -INFINITY, l = 0.f;
+    float o[8][4];  // o[c][j]: dim 16c + 4t + j of head g
+#pragma unroll
+    for (int c = 0; c < 8; ++c) o[c][0] = o[c][1] = o[c][2] = o[c][3] = 0.f;
+
+    bool timed_out = false;
+    for (int batch0 = 0; batch0 < ntiles && !timed_out; batch0 += kPidBatch) {
+      const int nb = ntiles - batch0 < kPidBatch ? ntiles - batch0 : kPidBatch;
+      __syncwarp();
+      for (int i = lane; i < nb; i += 32) {
+        const long long tok = t_begin + (long long)(batch0 + i) * kTileTokens;
+        long long pid = p.tables.at(b, tok / p.block_size);
+        if (pid < 0 || pid >= p.num_blocks) {
+          raise_status(p.status, MIE_STATUS_BAD_PAGE);
+          pid = 0;
+        }
+        pids[i] = (int)pid;
+      }
+      __syncwarp();
+      auto issue = [&](int i) {
+        const int s = i % kStages8;
+        uint8_t* dst = stages + (size_t)s * kStage8Bytes;
+        mbar_expect_tx(&bars[s], 2 * kTile8Bytes + 128);
+        tma_load_5d_hint(dst, &kvmap, &bars[s], 0, 0, 0, h, pids[i], stream_policy);
+        bulk_load_hint(dst + 2 * kTile8Bytes, kv.kv_scales + ((long long)pids[i] * p.kv_heads + h) * 32, 128,
+                       &bars[s], stream_policy);
+      };
+      if (lane == 0) {
+        for (int i = 0; i < kStages8 && i < nb; ++i) issue(i);
+      }
+      for (int i = 0; i < nb; ++i) {
+        const int s = i % kStages8;
+        const bool arrived = mbar_wait_bounded(&bars[s], (parity >> s) & 1u);
+        if (!__all_sync(0xffffffffu, arrived)) {
+          timed_out = true;
+          break;
+        }
+        parity ^= 1u << s;
+        uint8_t* stage = stages + (size_t)s * kStage8Bytes;
+        const uint32_t kbase = smem_u32(stage);
+        const uint32_t vbase = kbase + kTile8Bytes;
+        const float* scales = reinterpret_cast<const float*>(stage + 2 * kTile8Bytes);
+        const long long tok0 = t_begin + (long long)(batch0 + i) * kTileTokens;
+        const int valid = (int)(t_end - tok0 < kTileTokens ? t_end - tok0 : kTileTokens);
+
+        if (valid < kTileTokens) {
+          // Rows past the read length may hold anything (even NaN bytes): zero them in V so that
+          // 0 * V stays 0.  K rows and all scales of such rows are masked by selects below.
+          uint8_t* vt = stage + kTile8Bytes;
+          for (int c = lane; c < kTileTokens * 8; c += 32) {
+            if (c / 8 >= valid) *reinterpret_cast<uint4*>(vt + (c / 8) * 128 + (c % 8) * 16) = make_uint4(0, 0, 0, 0);
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+        }
+
+        // S = Q K^T for 16 tokens (two n-tiles), two accumulator sets to shorten the chain.
+        float sa[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        float sb[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) {  // chunks 2cp and 2cp + 1
+          const uint32_t addr = kbase + m_row + ((((uint32_t)(2 * cp) | m_sel) ^ m_key) << 4);
+          uint32_t r0, r1, r2, r3;
+          ldmatrix_x4(r0, r1, r2, r3, addr);
+          Mma16816<__half>::run(sa[0], qa[2 * cp][0], 0u, qa[2 * cp][1], 0u, e4m3x2_to_f16x2(r0),
+                                e4m3x2_to_f16x2(r0 >> 16));
+          Mma16816<__half>::run(sa[1], qa[2 * cp][0], 0u, qa[2 * cp][1], 0u, e4m3x2_to_f16x2(r1),
+                                e4m3x2_to_f16x2(r1 >> 16));
+          Mma16816<__half>::run(sb[0], qa[2 * cp + 1][0], 0u, qa[2 * cp + 1][1], 0u, e4m3x2_to_f16x2(r2),
+                                e4m3x2_to_f16x2(r2 >> 16));
+          Mma16816<__half>::run(sb[1], qa[2 * cp + 1][0], 0u, qa[2 * cp + 1][1], 0u, e4m3x2_to_f16x2(r3),
+                                e4m3x2_to_f16x2(r3 >> 16));
+        }
+        // This lane's four tokens of head g: 2t, 2t+1, 8+2t, 9+2t, and their K / V scales.
+        const int tk = 2 * t;
+        const float2 ks_lo = *reinterpret_cast<const float2*>(scales + tk);
+        const float2 ks_hi = *reinterpret_cast<const float2*>(scales + 8 + tk);
+        const float2 vs_lo = *reinterpret_cast<const float2*>(scales + 16 + tk);
+        const float2 vs_hi = *reinterpret_cast<const float2*>(scales + 24 + tk);
+        float sv[4], vs[4];
+        sv[0] = round_act<T>((sa[0][0] + sb[0][0]) * ks_lo.x) * p.scale_log2;
+        sv[1] = round_act<T>((sa[0][1] + sb[0][1]) * ks_lo.y) * p.scale_log2;
+        sv[2] = round_act<T>((sa[1][0] + sb[1][0]) * ks_hi.x) * p.scale_log2;
+        sv[3] = round_act<T>((sa[1][1] + sb[1][1]) * ks_hi.y) * p.scale_log2;
+        vs[0] = vs_lo.x, vs[1] = vs_lo.y, vs[2] = vs_hi.x, vs[3] = vs_hi.y;
+        if (tk >= valid) sv[0] = -INFINITY, vs[0] = 0.f;
+        if (tk + 1 >= valid) sv[1] = -INFINITY, vs[1] = 0.f;
+        if (tk + 8 >= valid) sv[2] = -INFINITY, vs[2] = 0.f;
+        if (tk + 9 >= valid) sv[3] = -INFINITY, vs[3] = 0.f;
+        float mx = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        float vmax = fmaxf(fmaxf(vs[0], vs[1]), fmaxf(vs[2], vs[3]));  // scales are >= 0
+        vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1));
+        vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 2));
+        vmax = fmaxf(vmax, 1e-30f);
+        const float m_new = fmaxf(m, mx);  // finite: token 0 of a tile is always valid
+        const float alpha = exp2f(m - m_new);
+        const float p0 = exp2f(sv[0] - m_new), p1 = exp2f(sv[1] - m_new);
+        const float p2 = exp2f(sv[2] - m_new), p3 = exp2f(sv[3] - m_new);
+        l = l * alpha + ((p0 + p1) + (p2 + p3));
+        m = m_new;
+        const float lift = __fdividef(1024.f, vmax), back = vmax * (1.f / 1024.f);
+        const uint32_t pa0 = Mma16816<__half>::pack(p0 * (vs[0] * lift), p1 * (vs[1] * lift));
+        const uint32_t pa2 = Mma16816<__half>::pack(p2 * (vs[2] * lift), p3 * (vs[3] * lift));
+        // O = O * alpha + (P' V8) * back
+#pragma unroll
+        for (int cp = 0; cp < 4; ++cp) {
+          const uint32_t addr = vbase + m_row + ((((uint32_t)(2 * cp) | m_sel) ^ m_key) << 4);
+          uint32_t r0, r1, r2, r3;
+          ldmatrix_x4_trans(r0, r1, r2, r3, addr);
+          // r0 / r1: tokens (2t, 2t+1) / (8+2t, 9+2t) x dims (2g, 2g+1) of chunk 2cp; r2 / r3: chunk 2cp + 1.
+          // Bytes (tok a dim e, tok a dim o, tok b dim e, tok b dim o) -> (a e, b e | a o, b o).
+          r0 = __byte_perm(r0, 0, 0x3120);
+          r1 = __byte_perm(r1, 0, 0x3120);
+          r2 = __byte_perm(r2, 0, 0x3120);
+          r3 = __byte_perm(r3, 0, 0x3120);
+          float xe[4] = {0.f, 0.f, 0.f, 0.f}, xo[4] = {0.f, 0.f, 0.f, 0.f};
+          float ye[4] = {0.f, 0.f, 0.f, 0.f}, yo[4] = {0.f, 0.f, 0.f, 0.f};
+          Mma16816<__half>::run(xe, pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r1));
+          Mma16816<__half>::run(xo, pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r0 >> 16), e4m3x2_to_f16x2(r1 >> 16));
+          Mma16816<__half>::run(ye, pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r3));
+          Mma16816<__half>::run(yo, pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r2 >> 16), e4m3x2_to_f16x2(r3 >> 16));
+          // Even-dimension tile: columns (2t, 2t+1) are dims 4t, 4t+2 of the chunk; odd tile: 4t+1, 4t+3.
+          float* oa = o[2 * cp];
+          float* ob = o[2 * cp + 1];
+          oa[0] = fmaf(xe[0], back, oa[0] * alpha);
+          oa[1] = fmaf(xo[0], back, oa[1] * alpha);
+          oa[2] = fmaf(xe[1], back, oa[2] * alpha);
+          oa[3] = fmaf(xo[1], back, oa[3] * alpha);
+          ob[0] = fmaf(ye[0], back, ob[0] * alpha);
+          ob[1] = fmaf(yo[0], back, ob[1] * alpha);
+          ob[2] = fmaf(ye[1], back, ob[2] * alpha);
+          ob[3] = fmaf(yo[1], back, ob[3] * alpha);
+        }
+        __syncwarp();
+        if (lane == 0 && i + kStages8 < nb) issue(i + kStages8);
+      }
+    }
+    if (timed_out) {
+      if (lane == 0) raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
+      break;
+    }
+
+    // Row sum over the quad, then write the result (final or partial).
+    l += __shfl_xor_sync(0xffffffffu, l, 1);
+    l += __shfl_xor_sync(0xffffffffu, l, 2);
+    const bool head_live = g < p.group;
+    const int head = h * p.group + (head_live ? g : 0);
+    if (nchunks == 1) {
+      const float inv = 1.f / fmaxf(l, 1.17549435e-38f);
+      T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)b * p.out.s[0] + (long long)head * p.out.s[1];
+      float amax = 0.f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          o[c][j] = round_act<T>(o[c][j] * inv);  // the stored (and quantised) value is the rounded one
+          amax = fmaxf(amax, fabsf(o[c][j]));
+        }
+        if (head_live) {
+          *reinterpret_cast<uint2*>(orow + c * 16 + 4 * t) =
+              make_uint2(Mma16816<T>::pack(o[c][0], o[c][1]), Mma16816<T>::pack(o[c][2], o[c][3]));
+        }
+      }
+      if (p.out_q8 != nullptr) {
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float scale = __fdiv_rn(amax, 448.0f), denom = fmaxf(scale, 1e-12f);
+        if (head_live) {
+          uint8_t* qrow = p.out_q8 + (long long)b * p.ldq8 + head * kHeadDim;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+                make_float2(__fdiv_rn(o[c][0], denom), __fdiv_rn(o[c][1], denom)), __NV_SATFINITE, __NV_E4M3);
+            const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+                make_float2(__fdiv_rn(o[c][2], denom), __fdiv_rn(o[c][3], denom)), __NV_SATFINITE, __NV_E4M3);
+            *reinterpret_cast<uint32_t*>(qrow + c * 16 + 4 * t) = (uint32_t)lo | ((uint32_t)hi << 16);
+          }
+          if (t == 0) p.out_scales[(long long)head * p.out_scale_ld + b] = scale;
+        }
+      }
+    } else {
+      const long long first_row = (long long)p.sc.offsets[b] * p.q_heads;
+      if (head_live) {
+        const long long row = first_row + (long long)ck * p.q_heads + head;
+        float* po = p.sc.part_o + row * kHeadDim;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          *reinterpret_cast<float4*>(po + c * 16 + 4 * t) = make_float4(o[c][0], o[c][1], o[c][2], o[c][3]);
+        }
+        if (t == 0) {
+          p.sc.part_m[row] = m;
+          p.sc.part_l[row] = l;
+        }
+      }
+    }
+  }
+
+  // Requests with nothing to read (rejected metadata) get zeros.
+  const int warps_total = gridDim.x * kWarps;
+  for (int e = blockIdx.x * kWarps + warp; e < p.batch; e += warps_total) {
+    if (p.sc.offsets[e + 1] != p.sc.offsets[e]) continue;
+    for (int hq = 0; hq < p.q_heads; ++hq) {
+      T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)e * p.out.s[0] + (long long)hq * p.out.s[1];
+      *reinterpret_cast<uint2*>(orow + 4 * lane) = make_uint2(0u, 0u);
+      if (p.out_q8 != nullptr) {
+        *reinterpret_cast<uint32_t*>(p.out_q8 + (long long)e * p.ldq8 + hq * kHeadDim + 4 * lane) = 0u;
+        if (lane == 0) p.out_scales[(long long)hq * p.out_scale_ld + e] = 0.f;
+      }
+    }
+  }
+}
+
 // Merge of split requests: one block per (request, KV head), exits at once when the request was not
 // split.  Each query head of the group gets W warps that share the request's chunks (W = 8 for small
 // batches, whose requests are cut into many chunks, 2 for large ones); their partial merges
@@ -808,6 +1139,140 @@ extern "C" int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mi
   if (int rc = page_tensor_map(value_blocks, num_blocks, kv_heads, block_size, dtype, &vmap)) return rc;
   if (dtype == MIE_DTYPE_BF16) return launch_fast<__nv_bfloat16>(p, kmap, vmap, stream);
   return launch_fast<__half>(p, kmap, vmap, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Decode attention over the e4m3 K/V pool
+// ---------------------------------------------------------------------------
+namespace mie {
+namespace {
+
+constexpr size_t kDecodeKv8Smem = (size_t)kWarps * kStages8 * kStage8Bytes + kWarps * kStages8 * 8 +
+                                  (size_t)kWarps * kPidBatch * 4 + 1024;
+
+struct Kv8MapKey {
+  const void* ptr;
+  long long page_stride;
+  int num_blocks, kv_heads;
+  bool operator==(const Kv8MapKey& o) const {
+    return ptr == o.ptr && page_stride == o.page_stride && num_blocks == o.num_blocks && kv_heads == o.kv_heads;
+  }
+};
+struct Kv8MapHash {
+  size_t operator()(const Kv8MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr);
+    h = h * 1000003u ^ (size_t)k.page_stride;
+    h = h * 1000003u ^ (size_t)(k.num_blocks * 131 + k.kv_heads);
+    return h;
+  }
+};
+
+// 5-D byte map over [pages][kv_heads][2][16][128]; one box = K and V rows of one (page, head) = 4 KiB.
+int kv8_tensor_map(const void* pool, long long page_stride, int num_blocks, int kv_heads, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<Kv8MapKey, CUtensorMap, Kv8MapHash> cache;
+  Kv8MapKey key{pool, page_stride, num_blocks, kv_heads};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+      *out = it->second;
+      return MIE_OK;
+    }
+  }
+  const uint64_t dims[5] = {(uint64_t)kHeadDim, (uint64_t)kTileTokens, 2, (uint64_t)kv_heads, (uint64_t)num_blocks};
+  const uint64_t strides[4] = {(uint64_t)kHeadDim, (uint64_t)kTile8Bytes, (uint64_t)(2 * kTile8Bytes),
+                               (uint64_t)page_stride};
+  const uint32_t box[5] = {(uint32_t)kHeadDim, (uint32_t)kTileTokens, 2, 1, 1};
+  const int rc = make_tensor_map(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 5, const_cast<void*>(pool), dims, strides, box,
+                                 CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != MIE_OK) return rc;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return MIE_OK;
+}
+
+template <typename T>
+int launch_kv8(const DecodeParams& p, const Kv8Params& kv, const CUtensorMap& kvmap, cudaStream_t stream) {
+  static bool configured[64] = {false};
+  int dev = 0;
+  MIE_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {
+    MIE_CUDA(cudaFuncSetAttribute(decode_kv8_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  (int)kDecodeKv8Smem));
+    configured[dev] = true;
+  }
+  MIE_CUDA(launch_chained(decode_kv8_kernel<T>, dim3(sm_count()), dim3(kWarps * 32), kDecodeKv8Smem, stream, kvmap, p,
+                          kv));
+  MIE_LAUNCH_CHECK("decode_kv8_kernel");
+  for (int g0 = 0; g0 < p.group; g0 += kMaxGroupMerge) {
+    DecodeParams q = p;
+    q.merge_head0 = g0;
+    const int heads = p.group - g0 < kMaxGroupMerge ? p.group - g0 : kMaxGroupMerge;
+    if (p.batch >= 128)
+      MIE_CUDA(launch_chained(merge_kernel<T, 2>, dim3(p.batch * p.kv_heads), dim3(heads * 2 * 32), 0, stream, q));
+    else
+      MIE_CUDA(launch_chained(merge_kernel<T, 8>, dim3(p.batch * p.kv_heads), dim3(heads * 8 * 32), 0, stream, q));
+    MIE_LAUNCH_CHECK("merge_kernel");
+  }
+  return MIE_OK;
+}
+
+}  // namespace
+}  // namespace mie
+
+extern "C" int mie_paged_decode_attention_kv8(mie_view4_t query, mie_view4_t out, const void* kv_pool,
+                                              int64_t page_stride_bytes, const float* kv_scales,
+                                              mie_index_t block_tables, mie_index_t sequence_lengths,
+                                              mie_index_t query_positions, int32_t batch, int32_t q_heads,
+                                              int32_t kv_heads, int32_t num_blocks, int32_t table_width,
+                                              int32_t dtype, float scale, int32_t split_policy, void* scratch,
+                                              int64_t scratch_bytes, int32_t plan_only, int32_t use_plan,
+                                              int32_t plan_slot, void* out_q8, int64_t ldq8, float* out_scales,
+                                              int32_t out_scale_ld, int32_t* status, void* stream_) {
+  cudaStream_t stream = (cudaStream_t)stream_;
+  MIE_CHECK_ARG(batch >= 0 && q_heads >= 1 && kv_heads >= 1 && q_heads % kv_heads == 0 && kv_heads <= 64,
+                "query heads (%d) must be a positive multiple of KV heads (%d)", q_heads, kv_heads);
+  MIE_CHECK_ARG(q_heads / kv_heads <= 8, "at most 8 query heads per KV head");
+  MIE_CHECK_ARG(num_blocks >= 1 && table_width >= 1, "invalid page geometry");
+  MIE_CHECK_ARG(dtype == MIE_DTYPE_BF16 || dtype == MIE_DTYPE_F16, "query / output must be bf16 or fp16");
+  MIE_CHECK_ARG(query.ptr && out.ptr && kv_pool && kv_scales && block_tables.ptr && sequence_lengths.ptr && scratch,
+                "null pointer");
+  MIE_CHECK_ARG(split_policy >= 0, "split_policy must be >= 0");
+  MIE_CHECK_ARG(plan_slot >= 0 && plan_slot < kCounters, "plan_slot must be in [0, %d)", kCounters);
+  MIE_CHECK_ARG(page_stride_bytes >= (long long)kv_heads * 2 * kTile8Bytes && page_stride_bytes % 16 == 0 &&
+                    (reinterpret_cast<uintptr_t>(kv_pool) & 1023) == 0 &&
+                    (reinterpret_cast<uintptr_t>(kv_scales) & 127) == 0,
+                "the e4m3 pool must be 1 KiB aligned with a page stride of at least kv_heads * 4096 bytes, "
+                "the scales 128-byte aligned");
+  MIE_CHECK_ARG(query.stride[3] == 1 && out.stride[3] == 1 && query.stride[0] % 4 == 0 && query.stride[1] % 4 == 0 &&
+                    out.stride[0] % 4 == 0 && out.stride[1] % 4 == 0 &&
+                    (reinterpret_cast<uintptr_t>(query.ptr) & 7) == 0 && (reinterpret_cast<uintptr_t>(out.ptr) & 7) == 0,
+                "query / output rows must be contiguous in head_dim and 8-byte aligned");
+  MIE_CHECK_ARG(out_q8 == nullptr || (out_scales != nullptr && out_scale_ld >= batch &&
+                                      ldq8 >= (long long)q_heads * kHeadDim),
+                "the quantised output needs scale storage and a row stride >= q_heads * 128");
+  MIE_CHECK_ARG((reinterpret_cast<uintptr_t>(scratch) & 255) == 0, "scratch must be 256-byte aligned");
+  if (batch == 0) return MIE_OK;
+  Scratch sc = carve(scratch, scratch_bytes, batch, q_heads, kv_heads, kHeadDim);
+  MIE_CHECK_ARG(sc.cap > batch, "scratch of %lld bytes is too small for batch %d", (long long)scratch_bytes, batch);
+
+  DecodeParams p{View4(query), View4(out), IndexView(block_tables), IndexView(sequence_lengths),
+                 IndexView(query_positions), sc, batch, q_heads, kv_heads, q_heads / kv_heads, kTileTokens, num_blocks,
+                 table_width, scale * 1.4426950408889634f, plan_slot, status, reinterpret_cast<uint8_t*>(out_q8), ldq8,
+                 out_scales, out_scale_ld, 0};
+  if (!use_plan) {
+    plan_kernel<<<1, kPlanThreads, 0, stream>>>(p.lengths, p.positions, batch, (long long)table_width * kTileTokens,
+                                                kv_heads, split_policy, target_seq_chunks(kv_heads), sc, status);
+    MIE_LAUNCH_CHECK("plan_kernel");
+  }
+  if (plan_only) return MIE_OK;
+  CUtensorMap kvmap;
+  if (int rc = kv8_tensor_map(kv_pool, page_stride_bytes, num_blocks, kv_heads, &kvmap)) return rc;
+  Kv8Params kv{kv_scales};
+  if (dtype == MIE_DTYPE_BF16) return launch_kv8<__nv_bfloat16>(p, kv, kvmap, stream);
+  return launch_kv8<__half>(p, kv, kvmap, stream);
 }
 
 // ---------------------------------------------------------------------------

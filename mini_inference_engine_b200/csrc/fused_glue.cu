@@ -177,6 +177,10 @@ struct QkvParams {
   int tokens, q_heads, kv_heads, block_size, num_blocks, table_rows, table_width;
   float eps;
   int* status;
+  // e4m3 K/V pool [pages][kv_heads][2][16][128] with scales [pages][kv_heads][2][16] (block_size 16), or null.
+  uint8_t* kv8_pool;
+  long long kv8_page_stride;  // bytes
+  float* kv8_scales;
 };
 
 __global__ void qkv_post_kernel(QkvParams p) {
@@ -246,6 +250,23 @@ __global__ void qkv_post_kernel(QkvParams p) {
     return;
   }
   const int kvh = is_v ? h - p.q_heads - p.kv_heads : h - p.q_heads;
+  if (p.kv8_pool != nullptr) {
+    // One scale per (token, KV head): amax of the 128 bf16 values / 448, the row divided by it and rounded
+    // to e4m3 (the activation quantiser's rule).
+    const __nv_bfloat162* pv = reinterpret_cast<const __nv_bfloat162*>(&result);
+    const float2 a = __bfloat1622float2(pv[0]), b2 = __bfloat1622float2(pv[1]);
+    const float amax = warp_max(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b2.x), fabsf(b2.y))));
+    const float scale = __fdiv_rn(amax, 448.0f), denom = fmaxf(scale, 1e-12f);
+    const __nv_fp8x2_storage_t lo = __nv_cvt_float2_to_fp8x2(
+        make_float2(__fdiv_rn(a.x, denom), __fdiv_rn(a.y, denom)), __NV_SATFINITE, __NV_E4M3);
+    const __nv_fp8x2_storage_t hi = __nv_cvt_float2_to_fp8x2(
+        make_float2(__fdiv_rn(b2.x, denom), __fdiv_rn(b2.y, denom)), __NV_SATFINITE, __NV_E4M3);
+    const int slot = (int)(pos % p.block_size);
+    uint8_t* row = p.kv8_pool + page * p.kv8_page_stride + ((long long)kvh * 2 + (is_v ? 1 : 0)) * 2048 + slot * 128;
+    *reinterpret_cast<uint32_t*>(row + lane * 4) = (uint32_t)lo | ((uint32_t)hi << 16);
+    if (lane == 0) p.kv8_scales[((page * p.kv_heads + kvh) * 2 + (is_v ? 1 : 0)) * 16 + slot] = scale;
+    return;
+  }
   const long long* st = is_v ? p.vb_s : p.kb_s;
   char* base = is_v ? p.value_blocks : p.key_blocks;
   __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(base) + page * st[0] + (long long)kvh * st[1] +
@@ -329,25 +350,17 @@ extern "C" int mie_rope(mie_view4_t x, const void* cos, const void* sin, int64_t
   return MIE_OK;
 }
 
-extern "C" int mie_qkv_norm_rope_write(const void* qkv, int64_t ld, const void* q_weight, const void* k_weight,
-                                       const void* cos_sin, int32_t max_pos, mie_index_t positions,
-                                       mie_index_t token_to_sequence, mie_index_t block_tables, void* q_out,
-                                       mie_view4_t key_blocks, mie_view4_t value_blocks, int32_t tokens,
-                                       int32_t q_heads, int32_t kv_heads, int32_t block_size, int32_t num_blocks,
-                                       int32_t table_rows, int32_t table_width, float eps, int32_t* status,
-                                       void* stream) {
-  MIE_CHECK_ARG(qkv && q_weight && k_weight && cos_sin && positions.ptr && block_tables.ptr && q_out &&
-                    key_blocks.ptr && value_blocks.ptr,
-                "null pointer");
-  MIE_CHECK_ARG(ld % 4 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 7) == 0 && key_blocks.stride[3] == 1 &&
-                    value_blocks.stride[3] == 1,
-                "qkv rows must be 8-byte aligned and pages contiguous in head_dim");
-  for (int i = 0; i < 3; ++i) {
-    MIE_CHECK_ARG(key_blocks.stride[i] % 4 == 0 && value_blocks.stride[i] % 4 == 0, "page strides must be multiples of 4");
-  }
+namespace {
+
+int launch_qkv_post(mie::QkvParams& p, const void* qkv, int64_t ld, const void* q_weight, const void* k_weight,
+                    const void* cos_sin, int32_t max_pos, const mie_index_t& positions,
+                    const mie_index_t& token_to_sequence, const mie_index_t& block_tables, void* q_out, int32_t tokens,
+                    int32_t q_heads, int32_t kv_heads, int32_t block_size, int32_t num_blocks, int32_t table_rows,
+                    int32_t table_width, float eps, int32_t* status, void* stream) {
+  MIE_CHECK_ARG(qkv && q_weight && k_weight && cos_sin && positions.ptr && block_tables.ptr && q_out, "null pointer");
+  MIE_CHECK_ARG(ld % 4 == 0 && (reinterpret_cast<uintptr_t>(qkv) & 7) == 0, "qkv rows must be 8-byte aligned");
   MIE_CHECK_ARG(tokens >= 0 && q_heads >= 1 && kv_heads >= 1 && max_pos >= 1, "invalid shape");
   if (tokens == 0) return MIE_OK;
-  QkvParams p;
   p.qkv = (const __nv_bfloat16*)qkv;
   p.ld = ld;
   p.q_weight = (const __nv_bfloat16*)q_weight;
@@ -358,12 +371,6 @@ extern "C" int mie_qkv_norm_rope_write(const void* qkv, int64_t ld, const void* 
   p.token_to_sequence = IndexView(token_to_sequence);
   p.tables = IndexView(block_tables);
   p.q_out = (__nv_bfloat16*)q_out;
-  p.key_blocks = (char*)key_blocks.ptr;
-  p.value_blocks = (char*)value_blocks.ptr;
-  for (int i = 0; i < 3; ++i) {
-    p.kb_s[i] = key_blocks.stride[i];
-    p.vb_s[i] = value_blocks.stride[i];
-  }
   p.tokens = tokens;
   p.q_heads = q_heads;
   p.kv_heads = kv_heads;
@@ -379,4 +386,55 @@ extern "C" int mie_qkv_norm_rope_write(const void* qkv, int64_t ld, const void* 
                           (cudaStream_t)stream, p));
   MIE_LAUNCH_CHECK("qkv_post_kernel");
   return MIE_OK;
+}
+
+}  // namespace
+
+extern "C" int mie_qkv_norm_rope_write(const void* qkv, int64_t ld, const void* q_weight, const void* k_weight,
+                                       const void* cos_sin, int32_t max_pos, mie_index_t positions,
+                                       mie_index_t token_to_sequence, mie_index_t block_tables, void* q_out,
+                                       mie_view4_t key_blocks, mie_view4_t value_blocks, int32_t tokens,
+                                       int32_t q_heads, int32_t kv_heads, int32_t block_size, int32_t num_blocks,
+                                       int32_t table_rows, int32_t table_width, float eps, int32_t* status,
+                                       void* stream) {
+  MIE_CHECK_ARG(key_blocks.ptr && value_blocks.ptr, "null pointer");
+  MIE_CHECK_ARG(key_blocks.stride[3] == 1 && value_blocks.stride[3] == 1, "pages must be contiguous in head_dim");
+  for (int i = 0; i < 3; ++i) {
+    MIE_CHECK_ARG(key_blocks.stride[i] % 4 == 0 && value_blocks.stride[i] % 4 == 0, "page strides must be multiples of 4");
+  }
+  QkvParams p;
+  p.key_blocks = (char*)key_blocks.ptr;
+  p.value_blocks = (char*)value_blocks.ptr;
+  for (int i = 0; i < 3; ++i) {
+    p.kb_s[i] = key_blocks.stride[i];
+    p.vb_s[i] = value_blocks.stride[i];
+  }
+  p.kv8_pool = nullptr;
+  p.kv8_page_stride = 0;
+  p.kv8_scales = nullptr;
+  return launch_qkv_post(p, qkv, ld, q_weight, k_weight, cos_sin, max_pos, positions, token_to_sequence, block_tables,
+                         q_out, tokens, q_heads, kv_heads, block_size, num_blocks, table_rows, table_width, eps,
+                         status, stream);
+}
+
+extern "C" int mie_qkv_norm_rope_write_kv8(const void* qkv, int64_t ld, const void* q_weight, const void* k_weight,
+                                           const void* cos_sin, int32_t max_pos, mie_index_t positions,
+                                           mie_index_t token_to_sequence, mie_index_t block_tables, void* q_out,
+                                           void* kv_pool, int64_t page_stride_bytes, float* kv_scales,
+                                           int32_t tokens, int32_t q_heads, int32_t kv_heads, int32_t num_blocks,
+                                           int32_t table_rows, int32_t table_width, float eps, int32_t* status,
+                                           void* stream) {
+  MIE_CHECK_ARG(kv_pool && kv_scales, "null pointer");
+  MIE_CHECK_ARG(page_stride_bytes >= (long long)kv_heads * 4096 && page_stride_bytes % 4 == 0 &&
+                    (reinterpret_cast<uintptr_t>(kv_pool) & 3) == 0,
+                "the e4m3 pool needs a page stride of at least kv_heads * 4096 bytes");
+  QkvParams p;
+  p.key_blocks = p.value_blocks = nullptr;
+  for (int i = 0; i < 3; ++i) p.kb_s[i] = p.vb_s[i] = 0;
+  p.kv8_pool = (uint8_t*)kv_pool;
+  p.kv8_page_stride = page_stride_bytes;
+  p.kv8_scales = kv_scales;
+  return launch_qkv_post(p, qkv, ld, q_weight, k_weight, cos_sin, max_pos, positions, token_to_sequence, block_tables,
+                         q_out, tokens, q_heads, kv_heads, /*block_size=*/16, num_blocks, table_rows, table_width, eps,
+                         status, stream);
 }

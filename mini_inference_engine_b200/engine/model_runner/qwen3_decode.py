@@ -36,6 +36,7 @@ import torch
 from ... import _lib
 from ..kernels import sm89_fp8
 from .peer_exchange import PeerExchange
+from ..kv_cache.fp8_kv import Fp8KvPool, launch_decode_attention_kv8
 from ..kv_cache.triton_flash_prefill import launch_flash_prefill
 from ..kv_cache.triton_paged_attention import decode_scratch, launch_decode_attention
 
@@ -509,7 +510,7 @@ class Qwen3DecodeRunner:
     def __init__(self, weights: Qwen3Weights, *, num_pages: int, max_batch: int, max_context: int,
                  process_group=None, kv_init: str = "zeros", fused_exchange: bool | None = None,
                  decode_buckets: tuple[int, ...] | None = None, chunk_buckets: tuple[int, ...] = (128, 512),
-                 max_chunks: int = 4) -> None:
+                 max_chunks: int = 4, kv_dtype: str = "bf16") -> None:
         self.weights, self.shape = weights, weights.shape
         self.device, self.group = weights.device, process_group
         self.tp = weights.tp_size
@@ -532,16 +533,33 @@ class Qwen3DecodeRunner:
         self.total_pages = num_pages + self.decode_buckets[-1] + chunk_scratch
         self.table_width = -(-max_context // shape.page)
         layers = len(weights.layers)
-        pool_shape = (layers, self.total_pages, self.local_kv_heads, shape.page, shape.head_dim)
-        self.key_blocks = torch.empty(pool_shape, dtype=torch.bfloat16, device=self.device)
-        self.value_blocks = torch.empty(pool_shape, dtype=torch.bfloat16, device=self.device)
-        if kv_init == "zeros":
-            self.key_blocks.zero_()
-            self.value_blocks.zero_()
-        elif kv_init == "normal":
-            for pool in (self.key_blocks, self.value_blocks):
+        if kv_dtype not in ("bf16", "fp8"):
+            raise ValueError("kv_dtype must be 'bf16' or 'fp8'")
+        self.kv_dtype = kv_dtype
+        self.kv8 = None
+        if kv_dtype == "fp8":
+            # Opt-in e4m3 K/V pool (one fp32 scale per token and KV head): decode steps only - the prompt
+            # kernels read bf16 pages.  bf16 stays the default and the parity path.
+            if shape.page != 16 or shape.head_dim != 128:
+                raise ValueError("the FP8 KV cache needs 16-token pages and head_dim 128")
+            self.kv8 = Fp8KvPool(layers, self.total_pages, self.local_kv_heads, self.device)
+            self.key_blocks = self.value_blocks = None
+            if kv_init == "normal":
                 for layer in range(layers):
-                    pool[layer].normal_()
+                    # random e4m3 bytes with the exponent capped (no NaN / huge values) and scales near 1 / 448
+                    self.kv8.data[layer].random_(0, 256).bitwise_and_(0xBF)
+                    self.kv8.scales[layer].uniform_(0.004, 0.012)
+        else:
+            pool_shape = (layers, self.total_pages, self.local_kv_heads, shape.page, shape.head_dim)
+            self.key_blocks = torch.empty(pool_shape, dtype=torch.bfloat16, device=self.device)
+            self.value_blocks = torch.empty(pool_shape, dtype=torch.bfloat16, device=self.device)
+            if kv_init == "zeros":
+                self.key_blocks.zero_()
+                self.value_blocks.zero_()
+            elif kv_init == "normal":
+                for pool in (self.key_blocks, self.value_blocks):
+                    for layer in range(layers):
+                        pool[layer].normal_()
         self.rope = rope_table(shape, max_context, self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.scratch = decode_scratch(max(max_batch, self.decode_buckets[-1]), self.local_q_heads,
@@ -636,6 +654,15 @@ class Qwen3DecodeRunner:
         """q/k RMSNorm + RoPE on the merged qkv rows, K/V rows to their page slots, q rows to ``queries``."""
 
         shape = self.shape
+        if self.kv8 is not None:
+            _lib.check(_lib.load().mie_qkv_norm_rope_write_kv8(
+                _lib.ptr(qkv), qkv.stride(0), _lib.ptr(layer.q_norm), _lib.ptr(layer.k_norm), _lib.ptr(self.rope),
+                int(self.rope.shape[0]), _lib.index_arg(positions), _lib.index_arg(token_to_sequence),
+                _lib.index_arg(block_tables), _lib.ptr(queries), _lib.ptr(self.kv8.data[layer_index]),
+                self.kv8.page_stride_bytes, _lib.ptr(self.kv8.scales[layer_index]), tokens, self.local_q_heads,
+                self.local_kv_heads, self.total_pages, table_rows, int(block_tables.shape[1]), shape.rms_eps,
+                _lib.ptr(self.status), _lib.stream_arg(self.device)))
+            return
         _lib.check(_lib.load().mie_qkv_norm_rope_write(
             _lib.ptr(qkv), qkv.stride(0), _lib.ptr(layer.q_norm), _lib.ptr(layer.k_norm), _lib.ptr(self.rope),
             int(self.rope.shape[0]), _lib.index_arg(positions), _lib.index_arg(token_to_sequence),
@@ -667,12 +694,18 @@ class Qwen3DecodeRunner:
             self._qkv_post(index, layer, qkv, queries, positions, None, block_tables, batch, batch)
             attended = torch.empty_like(queries)
             attn_q = self._quant_buffers(batch, lq * hd)
-            launch_decode_attention(queries, attended, self.key_blocks[index], self.value_blocks[index],
-                                    block_tables, sequence_lengths, None, scale=scale,
-                                    max_total_tokens=batch * self.max_context, scratch=self.scratch,
-                                    split_policy=1, use_plan=index % PLAN_SLOTS != 0,
-                                    plan_slot=index % PLAN_SLOTS, status=self.status,
-                                    quantized_out=attn_q)
+            if self.kv8 is not None:
+                launch_decode_attention_kv8(queries, attended, self.kv8.data[index], self.kv8.scales[index],
+                                            block_tables, sequence_lengths, None, scale=scale, scratch=self.scratch,
+                                            split_policy=1, use_plan=index % PLAN_SLOTS != 0,
+                                            plan_slot=index % PLAN_SLOTS, status=self.status, quantized_out=attn_q)
+            else:
+                launch_decode_attention(queries, attended, self.key_blocks[index], self.value_blocks[index],
+                                        block_tables, sequence_lengths, None, scale=scale,
+                                        max_total_tokens=batch * self.max_context, scratch=self.scratch,
+                                        split_policy=1, use_plan=index % PLAN_SLOTS != 0,
+                                        plan_slot=index % PLAN_SLOTS, status=self.status,
+                                        quantized_out=attn_q)
             _, residual, quantized = self._row_parallel_then_norm(attn_q, layer.o, layer.o_scale, batch, lq * hd,
                                                                   residual, layer.post_norm, quantize=True)
             gate_up = self._gemm(quantized, layer.gate_up, layer.gate_up_scale, batch, shape.hidden)
@@ -728,6 +761,9 @@ class Qwen3DecodeRunner:
         all other operators run once over the whole stream.  ``logit_rows`` selects the rows that are
         projected to logits; their greedy tokens are returned in that order."""
 
+        if self.kv8 is not None:
+            raise NotImplementedError("prompt chunks over the FP8 KV cache are not built: the prefill kernel reads "
+                                      "bf16 pages (kv_dtype='fp8' serves decode steps only)")
         shape, lib = self.shape, _lib.load()
         stream = _lib.stream_arg(self.device)
         tokens = int(input_ids.shape[0])

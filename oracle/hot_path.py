@@ -273,5 +273,37 @@ def rope_cos_sin(positions, head_dim, theta, dtype=torch.bfloat16):
     return emb.cos().to(dtype), emb.sin().to(dtype)
 
 
+def quantize_kv_rows(rows):
+    """FP8 KV cache: one scale per 128-wide K or V row, ``scale = amax / 448`` (raw scale kept, 0 for a zero
+    row), ``row / max(scale, 1e-12)`` rounded to e4m3 - the activation quantiser's rule (``quantize_activation``
+    above) applied per (token, KV head).  PARITY UNPINNED: the reference has no FP8 KV cache, it only names
+    the idea (docs/phase_notes/roofline.md:76).  ``rows``: ``[..., 128]`` bf16.  Returns (e4m3 bytes as uint8
+    ``[..., 128]``, fp32 scales ``[...]``)."""
+
+    values = rows.float()
+    scales = values.abs().amax(dim=-1) / 448.0
+    quantized = (values / scales.clamp_min(1e-12).unsqueeze(-1)).to(torch.float8_e4m3fn)
+    return quantized.view(torch.uint8), scales
+
+
+def dequantize_kv_rows(quantized_u8, scales, dtype=torch.bfloat16):
+    """What a reader of the FP8 cache sees, in the cache's former dtype: ``e4m3 * scale`` rounded to ``dtype``."""
+
+    return (quantized_u8.view(torch.float8_e4m3fn).float() * scales.unsqueeze(-1)).to(dtype)
+
+
+def paged_decode_attention_fp8_kv(query, key_blocks, value_blocks, block_tables, sequence_lengths, scale,
+                                  query_positions=None):
+    """Oracle of decode attention over an FP8 KV cache: the reference's torch path (``paged_decode_attention``)
+    fed the quantise -> dequantise image of the bf16 pages.  Returns the output and the two dequantised pools."""
+
+    k8, k_scales = quantize_kv_rows(key_blocks)
+    v8, v_scales = quantize_kv_rows(value_blocks)
+    keys = dequantize_kv_rows(k8, k_scales, key_blocks.dtype)
+    values = dequantize_kv_rows(v8, v_scales, value_blocks.dtype)
+    out = paged_decode_attention(query, keys, values, block_tables, sequence_lengths, scale, query_positions)
+    return out, keys, values
+
+
 def default_scale(head_dim):
     return 1.0 / math.sqrt(head_dim)

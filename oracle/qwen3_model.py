@@ -20,7 +20,7 @@ from . import hot_path
 
 
 def decode_step(weights, key_blocks, value_blocks, input_ids, sequence_lengths, block_tables, *, q_heads, kv_heads,
-                head_dim, eps, theta, return_hidden=False, all_reduce=None, pick_tokens=None):
+                head_dim, eps, theta, return_hidden=False, all_reduce=None, pick_tokens=None, kv_image=None):
     """``weights``: object with ``layers`` (each with qkv/o/gate_up/down e4m3 weights, ``*_scale`` block
     scales and the four norm vectors), ``embedding`` and ``final_norm``, all on the CPU.
     ``key_blocks`` / ``value_blocks``: ``[layers, pages, kv_heads, page, dim]``, updated in place.
@@ -28,7 +28,11 @@ def decode_step(weights, key_blocks, value_blocks, input_ids, sequence_lengths, 
 
     For a tensor-parallel shard pass the LOCAL head counts, ``all_reduce`` (sums a tensor over the ranks,
     applied after o_proj and down_proj, the only two exchange points) and ``pick_tokens`` (turns this
-    rank's vocabulary-sharded logits into global greedy tokens)."""
+    rank's vocabulary-sharded logits into global greedy tokens).
+
+    ``kv_image`` (FP8 KV cache, which the reference does not have): a function applied to the new K and V
+    rows before they are stored, e.g. quantise -> dequantise, so that the cache holds what an FP8 pool would
+    give back."""
 
     batch = input_ids.shape[0]
     hidden = weights.embedding.index_select(0, input_ids)
@@ -44,6 +48,8 @@ def decode_step(weights, key_blocks, value_blocks, input_ids, sequence_lengths, 
         k = hot_path.rms_norm(k.reshape(batch, 1, kv_heads, head_dim), layer.k_norm, eps).transpose(1, 2)
         v = v.reshape(batch, 1, kv_heads, head_dim).transpose(1, 2)
         q, k = hot_path.apply_rotary_pos_emb(q, k, cos, sin)
+        if kv_image is not None:
+            k, v = kv_image(k), kv_image(v)
         hot_path.write_decode_kv(k, v, block_tables, sequence_lengths, key_blocks[index], value_blocks[index])
         attended = hot_path.paged_decode_attention(q, key_blocks[index], value_blocks[index], block_tables,
                                                    sequence_lengths, 1.0 / math.sqrt(head_dim))
