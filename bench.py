@@ -49,6 +49,8 @@ def parse_args() -> argparse.Namespace:
     parser.add_argument("--no-e2e", action="store_true")
     parser.add_argument("--workload", default="config4", choices=["config4", "config3"],
                         help="config4: ragged decode sweep point (the headline); config3: 8 x (2048 prompt + 128 new)")
+    parser.add_argument("--no-extras", action="store_true",
+                        help="skip the extra keys measured after the headline (configs 0-3, FP8 KV cache)")
     parser.add_argument("--breakdown", action="store_true",
                         help="instead of the benchmark: CUDA-event time per kernel class of the eager decode step")
     parser.add_argument("--watchdog", type=int, default=900,
@@ -321,6 +323,101 @@ def run_breakdown(runner, buffers, steps: int, device, rank: int, world: int, co
               "classes": dict(sorted(classes.items(), key=lambda kv: -kv[1]["ms_per_step"]))})
 
 
+def measure_configs(weights, shape, device) -> dict:
+    """BASELINE configurations 0-3 next to the headline (configuration 4), each a few hundred milliseconds:
+    0 = paged decode attention on the 4-sequence ragged batch, 1 = the FP8 GEMMs at M = 256 / 2048,
+    2 = packed chunked-prefill attention, 3 = 8 requests x (2048-token prompt + 128 new tokens)."""
+
+    import types
+
+    import microbench
+    from mini_inference_engine_b200.engine.model_runner.qwen3_decode import Qwen3DecodeRunner
+
+    out = {}
+    ns = types.SimpleNamespace
+    d0 = microbench.decode(ns(concurrency=4, lengths=[17, 128, 513, 2048], tp=1, split_policy=1, kv_dtype="bf16",
+                              repeats=15), device)
+    out["config0"] = {"us_per_launch": d0["us_per_launch"], "gb_per_s": d0["gb_per_s"],
+                      "note": "4 sequences, 2,706 context tokens: launch-latency bound (11 MB of K/V)"}
+    gemms = {}
+    for name in ("qkv", "o", "gate_up", "down"):
+        for rows in (256, 2048):
+            g = microbench.gemm(ns(shape=name, rows=rows, copies=4, repeats=7), device)
+            gemms[f"{name}_m{rows}"] = {"us": g["us_per_launch"], "tflops": g["tflops"]}
+    out["config1"] = gemms
+    p2 = microbench.prefill(ns(requests=6, repeats=9), device)
+    out["config2"] = {"us_per_launch": p2["us_per_launch"], "tflops": p2["tflops"]}
+    requests, prompt_len, new_tokens = 8, 2048, 128
+    pages = requests * (-(-(prompt_len + new_tokens) // shape.page)) + 8
+    small = Qwen3DecodeRunner(weights, num_pages=pages, max_batch=requests, max_context=prompt_len + new_tokens + 8)
+    generator = torch.Generator().manual_seed(7)
+    prompts = [torch.randint(0, shape.vocab, (prompt_len,), generator=generator).tolist() for _ in range(requests)]
+    small.generate(prompts, new_tokens)  # warm-up; also captures the bucket's graph, as a server does at start-up
+    torch.cuda.synchronize(device)
+    t0 = time.perf_counter()
+    small.generate(prompts, new_tokens)
+    torch.cuda.synchronize(device)
+    wall = time.perf_counter() - t0
+    out["config3"] = {"output_tok_s": requests * new_tokens / wall, "seconds": wall,
+                      "includes": "packed prefill of 8 x 2048 tokens + 127 graph decode steps"}
+    small.release_graphs()
+    return out
+
+
+def measure_fp8_kv(weights, shape, device, contexts, tables, ids0, num_pages, max_context, steps, warmup, peak) -> dict:
+    """The headline workload again over the opt-in FP8 (e4m3) KV cache: same contexts, same block tables,
+    same graph step, K/V read as 2,112 bytes per token and layer instead of 4,096.  Not the headline: the
+    reference's cache precision is bf16."""
+
+    from mini_inference_engine_b200.engine.kv_cache.fp8_kv import launch_decode_attention_kv8
+    from mini_inference_engine_b200.engine.model_runner.qwen3_decode import Qwen3DecodeRunner
+
+    concurrency = int(contexts.numel())
+    runner = Qwen3DecodeRunner(weights, num_pages=num_pages, max_batch=concurrency, max_context=max_context,
+                               kv_init="normal", kv_dtype="fp8")
+    buffers = runner.capture(concurrency, tables.shape[1], advance=True)
+    buffers.input_ids.copy_(ids0.to(device))
+    buffers.block_tables.copy_(tables.to(device))
+    buffers.sequence_lengths.copy_((contexts + 1).to(torch.int32).to(device))
+    for _ in range(warmup):
+        runner.replay(concurrency, advance=True)
+    torch.cuda.synchronize(device)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        runner.replay(concurrency, advance=True)
+    end.record()
+    torch.cuda.synchronize(device)
+    runner.check_status()
+    step_ms = start.elapsed_time(end) / steps
+    lengths_now = (contexts + 1 + warmup + steps).to(torch.int32).to(device)
+    query = torch.randn(concurrency, shape.q_heads, 1, shape.head_dim, device=device).to(torch.bfloat16)
+    out = torch.empty_like(query)
+    durations = []
+    for layer in range(min(len(weights.layers), 12)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        launch_decode_attention_kv8(query, out, runner.kv8.data[layer], runner.kv8.scales[layer],
+                                    buffers.block_tables, lengths_now, None, scale=shape.head_dim ** -0.5,
+                                    scratch=runner.scratch, split_policy=1, status=runner.status)
+        e1.record()
+        if layer:
+            durations.append((e0, e1))
+    torch.cuda.synchronize(device)
+    attn_ms = statistics.mean(a.elapsed_time(b) for a, b in durations)
+    bytes_per_token = runner.kv8.bytes_per_token()
+    algorithmic = int(lengths_now.sum().item()) * bytes_per_token + 2 * query.numel() * 2
+    result = {"value": concurrency * steps / (step_ms * steps / 1e3), "unit": "tok/s", "ms_per_step": step_ms,
+              "kv_bytes_per_token_per_layer": bytes_per_token,
+              "attention": {"kernel": "decode_kv8_kernel<bf16>", "ms_per_launch": attn_ms,
+                            "algorithmic_bytes_per_launch": algorithmic,
+                            "achieved": algorithmic / (attn_ms / 1e3) / 1e9, "unit": "GB/s",
+                            "frac": algorithmic / (attn_ms / 1e3) / 1e9 / peak},
+              "note": "opt-in e4m3 KV cache with one fp32 scale per (token, KV head); bf16 KV stays the headline"}
+    runner.release_graphs()
+    return result
+
+
 def leave_together(runner, device) -> None:
     """End a multi-rank run: drop the captured graphs (they hold NCCL kernels and peer-memory pointers), wait
     for the device and for every rank, unmap the peers' exchange blocks, then exit without running the
@@ -560,6 +657,26 @@ def main() -> None:
             cpu = {"value": None, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
                    "sample": f"failed: {error!r}"}
 
+    extra_configs = extra_fp8 = None
+    if world == 1 and not args.no_extras and args.layers is None:
+        try:
+            extra_configs = measure_configs(weights, shape, device)
+        except Exception as error:  # extras are reported, never required
+            extra_configs = {"failed": repr(error)}
+        try:
+            import gc
+
+            tables_cpu, ids_cpu = tables, ids0
+            runner.release_graphs()
+            runner.key_blocks = runner.value_blocks = None
+            del buffers, tables_dev
+            gc.collect()
+            torch.cuda.empty_cache()
+            extra_fp8 = measure_fp8_kv(weights, shape, device, contexts, tables_cpu, ids_cpu, num_pages, max_context,
+                                       min(steps, 50), warmup, peak)
+        except Exception as error:
+            extra_fp8 = {"failed": repr(error)}
+
     if rank == 0:
         step_bytes = weights.weight_bytes() + total_tokens * kv_bytes_per_token * layers
         line = {
@@ -581,6 +698,7 @@ def main() -> None:
             "gpu_launches": launches_per_step * steps, "clocks": clocks, "tp_tokens_agree": tokens_agree,
             "step_hbm_bytes_per_gpu": step_bytes,
             "step_hbm_frac_of_peak": step_bytes / (elapsed_ms / steps / 1e3) / 1e9 / peak,
+            "configs": extra_configs, "fp8_kv": extra_fp8,
         }
         if args.layers is not None:
             line["invalid"] = "debug run with fewer layers"

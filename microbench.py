@@ -54,7 +54,11 @@ def _time(run, repeats: int, device: torch.device) -> float:
 
 
 def decode(args, device) -> dict:
-    lengths = workloads.lognormal_contexts(args.concurrency, seed=args.concurrency)
+    if getattr(args, "lengths", None):
+        lengths = torch.tensor([int(n) for n in args.lengths])  # e.g. BASELINE configuration 0: 17,128,513,2048
+        args.concurrency = len(lengths)
+    else:
+        lengths = workloads.lognormal_contexts(args.concurrency, seed=args.concurrency)
     total = int(lengths.sum())
     pages = sum(-(-int(n) // workloads.PAGE) for n in lengths) + 8
     tables = workloads.random_block_tables(lengths, num_pages=pages, seed=1).to(device)
@@ -161,6 +165,8 @@ def main() -> None:
     p.add_argument("--tp", type=int, default=1)
     p.add_argument("--split-policy", type=int, default=1)
     p.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"])
+    p.add_argument("--lengths", type=lambda text: [int(n) for n in text.split(",")], default=None,
+                   help="explicit context lengths instead of the log-normal draw, e.g. 17,128,513,2048")
     p = sub.add_parser("gemm")
     p.add_argument("--shape", default="qkv", choices=list(workloads.GEMM_SHAPES))
     p.add_argument("--rows", type=int, default=256)
