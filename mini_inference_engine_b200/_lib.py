@@ -210,7 +210,10 @@ def status_word(device: torch.device) -> torch.Tensor:
     index = device.index if device.index is not None else torch.cuda.current_device()
     word = _status_words.get(index)
     if word is None:
-        word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
+        # Created outside inference mode even when the first caller is inside it (the reference's engine runs
+        # under torch.inference_mode()): an inference tensor could not be cleared from ordinary code later.
+        with torch.inference_mode(False):
+            word = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", index))
         _status_words[index] = word
     return word
 

@@ -461,14 +461,16 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
 // Arithmetic.  The e4m3 bytes are widened to fp16 in registers (exact) and both products run as fp16
 // mma.sync with fp32 accumulation.  S = (q . k8) * k_scale[token]: the scale is applied to the fp32 dot
 // product.  O += P . (v8 * v_scale): the scale of token j is folded into its probability, normalised by the
-// largest V scale of the 16-token tile and lifted by 2^10 so that small probabilities stay normal fp16
-// numbers; the tile's product is then added into the running output with the inverse factor.
+// largest V scale seen so far (a running maximum R, handled like the running maximum of the softmax: when
+// it grows the accumulated output is rescaled) and lifted by 2^10 so that small probabilities stay normal
+// fp16 numbers; the accumulators hold O * 1024 / R and the factor is taken out at the end.
 // Fragment trick: ldmatrix hands a thread 4 consecutive bytes of a row; for Q.K^T they are taken as the
 // k-slots (2t, 2t+1 | 2t+8, 2t+9) of the MMA, with the query fragment read in the same permuted order
 // (a dot product does not care), and for P.V the transposed load yields two tokens x two adjacent
 // dimensions, which a byte permute splits into the B fragments of an "even dimensions" and an "odd
 // dimensions" n-tile.
-constexpr int kStages8 = 4;
+constexpr int kWarps8 = 16;  // more warps than the bf16 kernel: a tile is half the bytes for the same latency chain
+constexpr int kStages8 = 2;
 constexpr int kTile8Bytes = kTileTokens * kHeadDim;    // 2 KiB of K or of V
 constexpr int kStage8Bytes = 2 * kTile8Bytes + 1024;  // K + V + (128 bytes of scales, padded to the 1 KiB grid)
 
@@ -507,14 +509,14 @@ struct Kv8Params {
 };
 
 template <typename T>
-__global__ void __launch_bounds__(kWarps * 32, 1)
+__global__ void __launch_bounds__(kWarps8 * 32, 1)
     decode_kv8_kernel(const __grid_constant__ CUtensorMap kvmap, const DecodeParams p, const Kv8Params kv) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(align_up((long long)reinterpret_cast<uintptr_t>(smem_raw), 1024));
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* stages = smem + (size_t)warp * kStages8 * kStage8Bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps * kStages8 * kStage8Bytes) + warp * kStages8;
-  int* pids = reinterpret_cast<int*>(smem + (size_t)kWarps * kStages8 * kStage8Bytes + kWarps * kStages8 * 8) +
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)kWarps8 * kStages8 * kStage8Bytes) + warp * kStages8;
+  int* pids = reinterpret_cast<int*>(smem + (size_t)kWarps8 * kStages8 * kStage8Bytes + kWarps8 * kStages8 * 8) +
               warp * kPidBatch;
 
   if (lane == 0) {
@@ -568,9 +570,15 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     }
 
     float m = -INFINITY, l = 0.f;
-    float o[8][4];  // o[c][j]: dim 16c + 4t + j of head g
+    float vref = 1e-30f;  // running maximum of the V scales: the accumulators hold O * 1024 / vref
+    // MMA accumulators: oe[c] / oo[c] are the even- / odd-dimension n-tiles of chunk c; elements 0, 1 are
+    // head g's dims 16c + 4t (+2) resp. 16c + 4t + 1 (+2), elements 2, 3 belong to the padding rows.
+    float oe[8][4], oo[8][4];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) o[c][0] = o[c][1] = o[c][2] = o[c][3] = 0.f;
+    for (int c = 0; c < 8; ++c) {
+      oe[c][0] = oe[c][1] = oe[c][2] = oe[c][3] = 0.f;
+      oo[c][0] = oo[c][1] = oo[c][2] = oo[c][3] = 0.f;
+    }
 
     bool timed_out = false;
     for (int batch0 = 0; batch0 < ntiles && !timed_out; batch0 += kPidBatch) {
@@ -662,17 +670,26 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
         float vmax = fmaxf(fmaxf(vs[0], vs[1]), fmaxf(vs[2], vs[3]));  // scales are >= 0
         vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 1));
         vmax = fmaxf(vmax, __shfl_xor_sync(0xffffffffu, vmax, 2));
-        vmax = fmaxf(vmax, 1e-30f);
+        const float vref_new = fmaxf(vref, vmax);
         const float m_new = fmaxf(m, mx);  // finite: token 0 of a tile is always valid
         const float alpha = exp2f(m - m_new);
         const float p0 = exp2f(sv[0] - m_new), p1 = exp2f(sv[1] - m_new);
         const float p2 = exp2f(sv[2] - m_new), p3 = exp2f(sv[3] - m_new);
         l = l * alpha + ((p0 + p1) + (p2 + p3));
         m = m_new;
-        const float lift = __fdividef(1024.f, vmax), back = vmax * (1.f / 1024.f);
+        const float lift = __fdividef(1024.f, vref_new);
+        const float rescale = alpha * __fdividef(vref, vref_new);  // softmax maximum and V-scale reference moved
+        vref = vref_new;
         const uint32_t pa0 = Mma16816<__half>::pack(p0 * (vs[0] * lift), p1 * (vs[1] * lift));
         const uint32_t pa2 = Mma16816<__half>::pack(p2 * (vs[2] * lift), p3 * (vs[3] * lift));
-        // O = O * alpha + (P' V8) * back
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          oe[c][0] *= rescale;
+          oe[c][1] *= rescale;
+          oo[c][0] *= rescale;
+          oo[c][1] *= rescale;
+        }
+        // O += P' V8
 #pragma unroll
         for (int cp = 0; cp < 4; ++cp) {
           const uint32_t addr = vbase + m_row + ((((uint32_t)(2 * cp) | m_sel) ^ m_key) << 4);
@@ -684,23 +701,12 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
           r1 = __byte_perm(r1, 0, 0x3120);
           r2 = __byte_perm(r2, 0, 0x3120);
           r3 = __byte_perm(r3, 0, 0x3120);
-          float xe[4] = {0.f, 0.f, 0.f, 0.f}, xo[4] = {0.f, 0.f, 0.f, 0.f};
-          float ye[4] = {0.f, 0.f, 0.f, 0.f}, yo[4] = {0.f, 0.f, 0.f, 0.f};
-          Mma16816<__half>::run(xe, pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r1));
-          Mma16816<__half>::run(xo, pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r0 >> 16), e4m3x2_to_f16x2(r1 >> 16));
-          Mma16816<__half>::run(ye, pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r3));
-          Mma16816<__half>::run(yo, pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r2 >> 16), e4m3x2_to_f16x2(r3 >> 16));
           // Even-dimension tile: columns (2t, 2t+1) are dims 4t, 4t+2 of the chunk; odd tile: 4t+1, 4t+3.
-          float* oa = o[2 * cp];
-          float* ob = o[2 * cp + 1];
-          oa[0] = fmaf(xe[0], back, oa[0] * alpha);
-          oa[1] = fmaf(xo[0], back, oa[1] * alpha);
-          oa[2] = fmaf(xe[1], back, oa[2] * alpha);
-          oa[3] = fmaf(xo[1], back, oa[3] * alpha);
-          ob[0] = fmaf(ye[0], back, ob[0] * alpha);
-          ob[1] = fmaf(yo[0], back, ob[1] * alpha);
-          ob[2] = fmaf(ye[1], back, ob[2] * alpha);
-          ob[3] = fmaf(yo[1], back, ob[3] * alpha);
+          Mma16816<__half>::run(oe[2 * cp], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r0), e4m3x2_to_f16x2(r1));
+          Mma16816<__half>::run(oo[2 * cp], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r0 >> 16), e4m3x2_to_f16x2(r1 >> 16));
+          Mma16816<__half>::run(oe[2 * cp + 1], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r2), e4m3x2_to_f16x2(r3));
+          Mma16816<__half>::run(oo[2 * cp + 1], pa0, 0u, pa2, 0u, e4m3x2_to_f16x2(r2 >> 16),
+                                e4m3x2_to_f16x2(r3 >> 16));
         }
         __syncwarp();
         if (lane == 0 && i + kStages8 < nb) issue(i + kStages8);
@@ -716,6 +722,17 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
     l += __shfl_xor_sync(0xffffffffu, l, 2);
     const bool head_live = g < p.group;
     const int head = h * p.group + (head_live ? g : 0);
+    float o[8][4];  // o[c][j]: dim 16c + 4t + j of head g, with the V-scale reference taken out again
+    {
+      const float back = vref * (1.f / 1024.f);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        o[c][0] = oe[c][0] * back;
+        o[c][1] = oo[c][0] * back;
+        o[c][2] = oe[c][1] * back;
+        o[c][3] = oo[c][1] * back;
+      }
+    }
     if (nchunks == 1) {
       const float inv = 1.f / fmaxf(l, 1.17549435e-38f);
       T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)b * p.out.s[0] + (long long)head * p.out.s[1];
@@ -767,8 +784,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
   }
 
   // Requests with nothing to read (rejected metadata) get zeros.
-  const int warps_total = gridDim.x * kWarps;
-  for (int e = blockIdx.x * kWarps + warp; e < p.batch; e += warps_total) {
+  const int warps_total = gridDim.x * kWarps8;
+  for (int e = blockIdx.x * kWarps8 + warp; e < p.batch; e += warps_total) {
     if (p.sc.offsets[e + 1] != p.sc.offsets[e]) continue;
     for (int hq = 0; hq < p.q_heads; ++hq) {
       T* orow = reinterpret_cast<T*>(p.out.ptr) + (long long)e * p.out.s[0] + (long long)hq * p.out.s[1];
@@ -1147,8 +1164,8 @@ extern "C" int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mi
 namespace mie {
 namespace {
 
-constexpr size_t kDecodeKv8Smem = (size_t)kWarps * kStages8 * kStage8Bytes + kWarps * kStages8 * 8 +
-                                  (size_t)kWarps * kPidBatch * 4 + 1024;
+constexpr size_t kDecodeKv8Smem = (size_t)kWarps8 * kStages8 * kStage8Bytes + kWarps8 * kStages8 * 8 +
+                                  (size_t)kWarps8 * kPidBatch * 4 + 1024;
 
 struct Kv8MapKey {
   const void* ptr;
@@ -1203,7 +1220,7 @@ int launch_kv8(const DecodeParams& p, const Kv8Params& kv, const CUtensorMap& kv
                                   (int)kDecodeKv8Smem));
     configured[dev] = true;
   }
-  MIE_CUDA(launch_chained(decode_kv8_kernel<T>, dim3(sm_count()), dim3(kWarps * 32), kDecodeKv8Smem, stream, kvmap, p,
+  MIE_CUDA(launch_chained(decode_kv8_kernel<T>, dim3(sm_count()), dim3(kWarps8 * 32), kDecodeKv8Smem, stream, kvmap, p,
                           kv));
   MIE_LAUNCH_CHECK("decode_kv8_kernel");
   for (int g0 = 0; g0 < p.group; g0 += kMaxGroupMerge) {

@@ -212,9 +212,10 @@ class _RopeSwitch:
         if self.users == 0:
             targets = self._targets()
             self.original = targets[0].apply_rotary_pos_emb
+            entry = self.entry  # one function object for every module that binds the name
             for module in targets:
                 self.displaced.append((module, module.apply_rotary_pos_emb))
-                module.apply_rotary_pos_emb = self.entry
+                module.apply_rotary_pos_emb = entry
         self.users += 1
 
     def release(self) -> None:
