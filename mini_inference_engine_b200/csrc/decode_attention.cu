@@ -469,8 +469,8 @@ __global__ void __launch_bounds__(kWarps * 32, 1)
 // (a dot product does not care), and for P.V the transposed load yields two tokens x two adjacent
 // dimensions, which a byte permute splits into the B fragments of an "even dimensions" and an "odd
 // dimensions" n-tile.
-constexpr int kWarps8 = 16;  // more warps than the bf16 kernel: a tile is half the bytes for the same latency chain
-constexpr int kStages8 = 2;
+constexpr int kWarps8 = 12;  // more warps than the bf16 kernel: a tile is half the bytes for the same latency chain
+constexpr int kStages8 = 3;
 constexpr int kTile8Bytes = kTileTokens * kHeadDim;    // 2 KiB of K or of V
 constexpr int kStage8Bytes = 2 * kTile8Bytes + 1024;  // K + V + (128 bytes of scales, padded to the 1 KiB grid)
 
