@@ -302,8 +302,9 @@ int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void* q, int64_t
  * x8 [m, k] e4m3 (row stride ldx bytes), a_scale as mie_fp8_quantize writes it,
  * w8 [n, k] e4m3 (row stride ldw bytes), w_scale [ceil(n/128), w_scale_ld].
  * Operand base pointers and row strides must be multiples of 16 bytes.
- * Up to 128 tokens run with the weight rows as the 128 MMA rows (a weight
- * streaming loop); more tokens run a persistent 128 x 256-tile kernel.
+ * Up to 128 tokens (up to 256 when n <= 1536) run with the weight rows as the
+ * 128 MMA rows (a weight streaming loop); more tokens run a persistent
+ * 128 x 256-tile kernel.
  *
  * Summation order.  Within one CTA the K blocks are added in increasing order.
  * When a shape has fewer output tiles than SMs - or, above 128 tokens, when the

@@ -1080,8 +1080,12 @@ extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, i
 
   // Up to 128 tokens stream the weights through the narrow kernel, unless that needs a second wave of
   // full-K tiles (more 128-row weight tiles than SMs at more than 32 tokens, where only one of its CTAs
-  // fits an SM: gate_up): the wide kernel's 256-row tiles then finish in one round.
-  const bool narrow = m <= 128 && !(m > 32 && (n + kTileR - 1) / kTileR > sm_count());
+  // fits an SM: gate_up): the wide kernel's 256-row tiles then finish in one round.  Between 129 and 256
+  // tokens a weight of at most 12 row tiles (N <= 1536: the merged qkv of a 4- or 8-way head shard) is
+  // still faster there, as two token tiles (measured 9.7 vs 12.6 us at N = 768, 10.8 vs 13.1 at N = 1536;
+  // at N = 2560 the wide kernel wins).
+  const int tiles_w = (n + kTileR - 1) / kTileR;
+  const bool narrow = (m <= 128 && !(m > 32 && tiles_w > sm_count())) || (m <= 256 && tiles_w <= 12);
   const int kb = (k + kBlockK - 1) / kBlockK;
 
   GemmParams p;
