@@ -7,6 +7,7 @@ loaded, every operator of this package raises ``MieLibraryError``.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, c_char_p, c_float, c_int32, c_int64, c_void_p
 from pathlib import Path
 
@@ -136,7 +137,10 @@ def exported_symbols() -> tuple[str, ...]:
 
 
 def library_path() -> Path:
-    return LIB_PATH
+    """The shared library to load: ``$MIE_LIBRARY_PATH`` when set (a build kept elsewhere), else the in-tree one."""
+
+    override = os.environ.get("MIE_LIBRARY_PATH")
+    return Path(override) if override else LIB_PATH
 
 
 def load() -> ctypes.CDLL:
@@ -145,20 +149,21 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    path = library_path()
+    if not path.exists():
         raise MieLibraryError(
-            f"{LIB_PATH} is missing: run `python -m mini_inference_engine_b200.build` (needs nvcc). "
+            f"{path} is missing: run `python -m mini_inference_engine_b200.build` (needs nvcc). "
             "This package has no CPU or PyTorch fallback."
         )
     try:
-        lib = ctypes.CDLL(str(LIB_PATH))
+        lib = ctypes.CDLL(str(path))
     except OSError as error:
-        raise MieLibraryError(f"cannot load {LIB_PATH}: {error}") from error
+        raise MieLibraryError(f"cannot load {path}: {error}") from error
     for name, (restype, argtypes) in _SIGNATURES.items():
         try:
             fn = getattr(lib, name)
         except AttributeError as error:
-            raise MieLibraryError(f"{LIB_PATH} does not export {name}; rebuild it") from error
+            raise MieLibraryError(f"{path} does not export {name}; rebuild it") from error
         fn.restype = restype
         fn.argtypes = argtypes
     _lib = lib

@@ -98,12 +98,28 @@ __device__ __forceinline__ long long block_sum_ll(long long v, long long* smem) 
   return t;
 }
 
+// Split-KV planning.  The decode kernel is a dynamic queue of (request, chunk, KV head) items over
+// `warps` persistent warps, so its time is close to
+//     ceil(items / warps) x (time of one chunk + what a warp loses between two items),
+// with items = kv_heads x sum_b ceil(length_b / chunk).  Policy 1 evaluates that with the batch's real
+// lengths for a grid of chunk sizes and takes the cheapest: a chunk size that just misses a whole number of
+// rounds costs a full extra round on a few warps.  `switch_tokens` is the between-items loss (queue pop,
+// metadata, refilling the TMA ring, writing and later merging a partial) expressed in tokens of streaming;
+// 128 tokens of one bf16 KV head (64 KB) reproduces the measured ranking of chunk sizes on an 8-way
+// head shard (384 and 1024 tokens best, 512 and 192 worst).
+constexpr int kPlanCands = 21;
+__constant__ int kPlanChunks[kPlanCands] = {64,  80,  96,  112, 128, 160, 192,  224,  256,  320, 384,
+                                            448, 512, 640, 768, 896, 1024, 1280, 1536, 1792, 2048};
+
 __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, IndexView positions, int batch,
                                                             long long capacity_tokens, int kv_heads, int policy,
-                                                            int target_seq_chunks, Scratch sc, int* status) {
+                                                            int warps, int switch_tokens, Scratch sc, int* status) {
   __shared__ long long red[32];
   __shared__ int warp_tot[32];
-  __shared__ int running_s;
+  __shared__ int cand_part[32][kPlanCands];
+  __shared__ int cand_count[kPlanCands];
+  __shared__ int running_s, running_r;
+  __shared__ long long chunk_s;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   chain_wait();
   chain_release();
@@ -111,25 +127,61 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
   long long local = 0;
   for (int b = tid; b < batch; b += blockDim.x) local += read_length(lengths, positions, b, capacity_tokens, status);
   const long long total = block_sum_ll(local, red);
+  const long long room = sc.cap - batch;  // > 0, checked on the host
 
   long long chunk;
   if (policy == 0) {
     chunk = (1ll << 40);
   } else if (policy == 1) {
-    chunk = (total + target_seq_chunks - 1) / target_seq_chunks;
-    chunk = align_up(chunk, kTileTokens);
-    if (chunk < kMinChunk) chunk = kMinChunk;
-    if (chunk > kMaxChunk) chunk = kMaxChunk;
+    int mine[kPlanCands];
+#pragma unroll
+    for (int j = 0; j < kPlanCands; ++j) mine[j] = 0;
+    for (int b = tid; b < batch; b += blockDim.x) {
+      const int rl = (int)read_length(lengths, positions, b, capacity_tokens, nullptr);
+#pragma unroll
+      for (int j = 0; j < kPlanCands; ++j) mine[j] += (rl + kPlanChunks[j] - 1) / kPlanChunks[j];
+    }
+#pragma unroll
+    for (int j = 0; j < kPlanCands; ++j) {
+      int v = mine[j];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) cand_part[warp][j] = v;
+    }
+    __syncthreads();
+    if (tid < kPlanCands) {
+      int t = 0;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += cand_part[w][tid];
+      cand_count[tid] = t;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      long long best = kPlanChunks[kPlanCands - 1];
+      long long best_cost = -1;
+      for (int j = kPlanCands - 1; j >= 0; --j) {  // larger chunks first: they win ties (fewer partials)
+        if (cand_count[j] > sc.cap) continue;      // more (request, chunk) pairs than the scratch holds
+        const long long items = (long long)cand_count[j] * kv_heads;
+        const long long rounds = (items + warps - 1) / warps;
+        const long long cost = rounds * (kPlanChunks[j] + switch_tokens);
+        if (best_cost < 0 || cost < best_cost) {
+          best_cost = cost;
+          best = kPlanChunks[j];
+        }
+      }
+      chunk_s = best;
+    }
+    __syncthreads();
+    chunk = chunk_s;
   } else {
     chunk = align_up(policy, kTileTokens);
   }
   // Never emit more (request, chunk) pairs than the caller's scratch holds.
-  const long long room = sc.cap - batch;  // > 0, checked on the host
   if (total / chunk + batch > sc.cap) {
     chunk = align_up((total + room - 1) / room, kTileTokens);  // still exact, only coarser
   }
 
-  if (tid == 0) running_s = 0;
+  // Pass 1: offsets[b] = first (request, chunk) pair of request b (the rows of its partial results).
+  if (tid == 0) running_s = running_r = 0;
   __syncthreads();
   for (int base = 0; base < batch; base += blockDim.x) {
     const int b = base + tid;
@@ -148,14 +200,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
     __syncthreads();
     int before = running_s;
     for (int w = 0; w < warp; ++w) before += warp_tot[w];
-    const int excl = before + incl - c;
-    if (b < batch) {
-      sc.offsets[b] = excl;
-      for (int j = 0; j < c; ++j) {
-        sc.item_seq[excl + j] = b;
-        sc.item_chunk[excl + j] = j;
-      }
-    }
+    if (b < batch) sc.offsets[b] = before + incl - c;
     __syncthreads();
     if (tid == 0) {
       int t = 0;
@@ -164,11 +209,58 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
     }
     __syncthreads();
   }
+  const int pairs = running_s;
+  // Requests that have at least one chunk.
+  int live_local = 0;
+  for (int b = tid; b < batch; b += blockDim.x) {
+    live_local += read_length(lengths, positions, b, capacity_tokens, nullptr) > 0 ? 1 : 0;
+  }
+  const int live = (int)block_sum_ll(live_local, red);
+
+  // Pass 2: the work list.  Every chunk but a request's last is full-sized; those come first (in request
+  // order), the last chunks - mostly partial, so shorter - after them, so that the queue ends on its
+  // smallest items.
+  for (int base = 0; base < batch; base += blockDim.x) {
+    const int b = base + tid;
+    int c = 0;
+    if (b < batch) {
+      const long long rl = read_length(lengths, positions, b, capacity_tokens, nullptr);
+      c = (int)((rl + chunk - 1) / chunk);
+    }
+    const int flag = c > 0 ? 1 : 0;
+    int incl = flag;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) warp_tot[warp] = incl;
+    __syncthreads();
+    int before = running_r;
+    for (int w = 0; w < warp; ++w) before += warp_tot[w];
+    const int rank = before + incl - flag;  // requests with chunks in front of b
+    if (b < batch && c > 0) {
+      const int first = sc.offsets[b] - rank;  // full-sized chunks in front of b
+      for (int j = 0; j + 1 < c; ++j) {
+        sc.item_seq[first + j] = b;
+        sc.item_chunk[first + j] = j;
+      }
+      sc.item_seq[pairs - live + rank] = b;
+      sc.item_chunk[pairs - live + rank] = c - 1;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int t = 0;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += warp_tot[w];
+      running_r += t;
+    }
+    __syncthreads();
+  }
   if (tid == 0) {
-    sc.offsets[batch] = running_s;
+    sc.offsets[batch] = pairs;
     sc.header[0] = (int)(chunk > 0x7fffffffll ? 0x7fffffff : chunk);
-    sc.header[1] = running_s;
-    sc.header[2] = running_s * kv_heads;
+    sc.header[1] = pairs;
+    sc.header[2] = pairs * kv_heads;
   }
   if (tid < kCounters) sc.header[kCounterBase + tid] = 0;
 }
@@ -1004,12 +1096,10 @@ long long fixed_scratch_bytes(int batch, int kv_heads) {
 }
 long long per_chunk_bytes(int q_heads, int head_dim) { return 8 + (long long)q_heads * (head_dim + 2) * 4; }
 
-// (request, chunk) pairs the plan aims for.  Four work items per warp balance the tail of the dynamic queue
-// well when an item is hundreds of KB; with a single KV head per rank (8-way head sharding) an item of
-// that count is only ~80 KB and the ~3 us a warp spends between two items (queue pop, metadata, refilling
-// its TMA ring) shows: two larger items per warp measured 12-15 % faster there.
+// (request, chunk) pairs `mie_decode_scratch_bytes` makes room for beyond one per request: four items per
+// warp.  The plan kernel considers more items per warp only while they fit the scratch it was given.
 int target_seq_chunks(int kv_heads) {
-  const int items = sm_count() * kWarps * (kv_heads >= 2 ? 4 : 2);
+  const int items = sm_count() * kWarps * 4;
   return (items + kv_heads - 1) / kv_heads;
 }
 
@@ -1150,7 +1240,7 @@ extern "C" int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mi
                  out_scales, out_scale_ld, 0};
   if (!use_plan) {
     plan_kernel<<<1, kPlanThreads, 0, stream>>>(p.lengths, p.positions, batch, (long long)table_width * block_size,
-                                                kv_heads, split_policy, target_seq_chunks(kv_heads), sc, status);
+                                                kv_heads, split_policy, sm_count() * kWarps, 128, sc, status);
     MIE_LAUNCH_CHECK("plan_kernel");
   }
   if (plan_only) return MIE_OK;
@@ -1285,7 +1375,7 @@ extern "C" int mie_paged_decode_attention_kv8(mie_view4_t query, mie_view4_t out
                  out_scales, out_scale_ld, 0};
   if (!use_plan) {
     plan_kernel<<<1, kPlanThreads, 0, stream>>>(p.lengths, p.positions, batch, (long long)table_width * kTileTokens,
-                                                kv_heads, split_policy, target_seq_chunks(kv_heads), sc, status);
+                                                kv_heads, split_policy, sm_count() * kWarps8, 256, sc, status);
     MIE_LAUNCH_CHECK("plan_kernel");
   }
   if (plan_only) return MIE_OK;

@@ -578,8 +578,11 @@ class Qwen3DecodeRunner:
             fused_exchange = os.environ.get("MIE_TP_EXCHANGE", "fused") != "nccl"
         self.exchange = None
         if self.tp > 1 and fused_exchange:
-            self.exchange = PeerExchange(self.tp, weights.tp_rank, max(max_batch, self.decode_buckets[-1]),
-                                         shape.hidden, self.device, process_group)
+            # Rows for the largest decode bucket plus the largest prompt-chunk bucket of a mixed step; a longer
+            # flat forward (a whole-prompt prefill) sums its partial rows with NCCL instead.
+            exchange_rows = max(max_batch, self.decode_buckets[-1]) + max(self.chunk_buckets, default=0)
+            self.exchange = PeerExchange(self.tp, weights.tp_rank, exchange_rows, shape.hidden, self.device,
+                                         process_group)
 
     # -- small helpers ------------------------------------------------------------------------
 
@@ -772,14 +775,14 @@ class Qwen3DecodeRunner:
         hd, lq = shape.head_dim, self.local_q_heads
         launches_before = lib.mie_launch_count()
         hidden = self.weights.embedding.index_select(0, input_ids)
-        residual, mlp_out = None, None
         scale = 1.0 / math.sqrt(hd)
-        for index, layer in enumerate(self.weights.layers):
-            if index == 0:
-                _, _, quantized = self._norm(hidden, layer.input_norm, quantize=True)
-                residual = hidden
-            else:
-                _, residual, quantized = self._norm(mlp_out, layer.input_norm, residual, quantize=True)
+        layers = self.weights.layers
+        # Same layer structure as the decode forward: every residual add + RMSNorm (+ quantisation) is fused
+        # with the sum over the ranks that precedes it (the peer-memory exchange when the token count fits its
+        # buffers, NCCL all-reduce + the norm kernel otherwise).
+        _, _, quantized = self._norm(hidden, layers[0].input_norm, quantize=True)
+        residual, normed = hidden, None
+        for index, layer in enumerate(layers):
             qkv = self._gemm(quantized, layer.qkv, layer.qkv_scale, tokens, shape.hidden)
             queries = torch.empty(tokens, lq, hd, dtype=torch.bfloat16, device=self.device)
             self._qkv_post(index, layer, qkv, queries, token_positions, token_to_sequence, block_tables, tokens,
@@ -797,13 +800,16 @@ class Qwen3DecodeRunner:
                                      self.value_blocks[index], block_tables[decode_rows:], cu_seqlens, kv_lens,
                                      max_query_len=max_query_len, scale=scale, status=self.status)
             attn_q = self._quantize(attended.view(tokens, lq * hd))
-            attn_out = self._all_reduce(self._gemm(attn_q, layer.o, layer.o_scale, tokens, lq * hd))
-            _, residual, quantized = self._norm(attn_out, layer.post_norm, residual, quantize=True)
+            _, residual, quantized = self._row_parallel_then_norm(attn_q, layer.o, layer.o_scale, tokens, lq * hd,
+                                                                  residual, layer.post_norm, quantize=True)
             gate_up = self._gemm(quantized, layer.gate_up, layer.gate_up_scale, tokens, shape.hidden)
             act_q = self._silu_mul_quantized(gate_up, tokens)
-            mlp_out = self._all_reduce(self._gemm(act_q, layer.down, layer.down_scale, tokens, self.local_inter))
-        final, _, _ = self._norm(mlp_out.index_select(0, logit_rows), self.weights.final_norm,
-                                 residual.index_select(0, logit_rows), quantize=False)
+            last = index + 1 == len(layers)
+            next_norm = self.weights.final_norm if last else layers[index + 1].input_norm
+            normed, residual, quantized = self._row_parallel_then_norm(act_q, layer.down, layer.down_scale, tokens,
+                                                                       self.local_inter, residual, next_norm,
+                                                                       quantize=not last)
+        final = normed.index_select(0, logit_rows)
         if self.fused_lm_head and not return_logits and final.shape[0] <= 256:
             picked = self.greedy_tokens(final)
             self.launches_per_step = int(lib.mie_launch_count() - launches_before)

@@ -39,7 +39,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, results) -> None:
+def _worker(rank: int, world: int, port: int, results, mixed: bool) -> None:
     import torch.distributed as dist
 
     from mini_inference_engine_b200.engine.model_runner.continuous import ContinuousBatcher
@@ -56,13 +56,19 @@ def _worker(rank: int, world: int, port: int, results) -> None:
         runner = Qwen3DecodeRunner(weights, num_pages=32, max_batch=4, max_context=128,
                                    process_group=dist.group.WORLD)
         assert runner.exchange is not None
-        batcher = ContinuousBatcher(runner, max_prefill_tokens=128)
-        for request in _requests():
-            batcher.submit(*request)
+        batcher = ContinuousBatcher(runner, max_prefill_tokens=128, mixed=mixed)
+        first, late, third = _requests()
+        batcher.submit(*first)
+        batcher.submit(*third)
+        for _ in range(3):
+            batcher.step()
+        batcher.submit(*late)  # its 70-token prompt arrives while the other two decode
         tokens = batcher.run()
-        replays = sum(1 for record in batcher.records if "bucket" in record)
+        replays = sum(1 for record in batcher.records if "bucket" in record or record["kind"] == "mixed")
+        mixed_steps = sum(1 for record in batcher.records if record["kind"] == "mixed" and record["decode_rows"])
         status = int(runner.status.item())
         outcome = {"tokens": {rid: list(t) for rid, t in tokens.items()}, "replays": replays, "status": status,
+                   "mixed_steps": mixed_steps,
                    "window": (weights.inter_window, weights.inter_offset, weights.inter_width)}
         runner.release_graphs()
         torch.cuda.synchronize(device)
@@ -76,8 +82,9 @@ def _worker(rank: int, world: int, port: int, results) -> None:
         os._exit(0 if outcome and "error" not in outcome else 1)
 
 
+@pytest.mark.parametrize("mixed", [False, True])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_every_rank_matches_the_unsharded_oracle(world):
+def test_every_rank_matches_the_unsharded_oracle(world, mixed):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
@@ -92,7 +99,7 @@ def test_every_rank_matches_the_unsharded_oracle(world):
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(rank, world, port, results)) for rank in range(world)]
+    procs = [ctx.Process(target=_worker, args=(rank, world, port, results, mixed)) for rank in range(world)]
     for proc in procs:
         proc.start()
     for proc in procs:
@@ -106,6 +113,8 @@ def test_every_rank_matches_the_unsharded_oracle(world):
     for rank, outcome in enumerate(outcomes):
         assert outcome["status"] == 0, (rank, outcome["status"])
         assert outcome["replays"] >= 4
+        # With mixed steps the late prompt rides along with the two decoding rows through the fused exchange.
+        assert (outcome["mixed_steps"] >= 1) == mixed
         assert outcome["tokens"] == expected, (rank, outcome["tokens"], expected)
     if world == 8:  # odd ranks start in the middle of a scale block
         assert outcomes[1]["window"] == (256, 64, 192) and outcomes[0]["window"] == (256, 0, 192)
