@@ -194,6 +194,31 @@ def use_all_host_cores() -> int:
     return torch.get_num_threads()
 
 
+def cpu_baseline_in_clean_process(args: argparse.Namespace) -> dict:
+    """Run ``bench.py --impl reference`` in a child process whose environment carries no thread limits and no
+    rendezvous variables, and return its JSON line.  A multi-process launcher exports ``OMP_NUM_THREADS=1``
+    before Python starts; raising the thread count afterwards leaves the OpenMP pool of that process pinned
+    the way it was initialised (measured: 40x slower than a clean process, not 1x), so the baseline that has
+    to be the same at every N is taken in a process of its own."""
+
+    drop = ("OMP_NUM_THREADS", "MKL_NUM_THREADS", "OPENBLAS_NUM_THREADS", "RANK", "LOCAL_RANK", "WORLD_SIZE",
+            "LOCAL_WORLD_SIZE", "GROUP_RANK", "ROLE_RANK", "MASTER_ADDR", "MASTER_PORT", "TORCHELASTIC_RUN_ID")
+    env = {k: v for k, v in os.environ.items() if k not in drop and not k.startswith("TORCHELASTIC")}
+    env["MIE_BENCH_CPU_CHILD"] = "1"
+    env["CUDA_VISIBLE_DEVICES"] = ""
+    done = subprocess.run([sys.executable, str(Path(__file__).resolve()), "--impl", "reference", "--gpus",
+                           str(args.gpus), "--steps", str(args.steps), "--warmup", str(args.warmup)],
+                          env=env, capture_output=True, text=True, timeout=900)
+    lines = [line for line in done.stdout.splitlines() if line.startswith("{")]
+    if done.returncode != 0 or not lines:
+        raise RuntimeError(f"CPU baseline child failed ({done.returncode}): {done.stderr[-400:]}")
+    return json.loads(lines[-1])
+
+
+def launched_with_thread_limit() -> bool:
+    return "OMP_NUM_THREADS" in os.environ and os.environ.get("MIE_BENCH_CPU_CHILD") != "1"
+
+
 def run_reference_arm(args: argparse.Namespace) -> None:
     """The reference's own CPU path for this metric: its torch block-wise attention and the FP8 linear
     restated on the CPU (the reference has no CPU FP8 kernel), on all host threads."""
@@ -203,6 +228,9 @@ def run_reference_arm(args: argparse.Namespace) -> None:
         return
     # A multi-process launcher exports OMP_NUM_THREADS=1 to its workers; the baseline uses every host core
     # at every N so that all runs share one denominator.
+    if launched_with_thread_limit():
+        emit(cpu_baseline_in_clean_process(args))
+        return
     use_all_host_cores()
     repeats = max(1, min(args.steps, 2))
     started = time.perf_counter()
@@ -560,30 +588,37 @@ def main() -> None:
     # ---- end to end: host metadata in, H2D, replay, D2H of the sampled tokens, every step ----
     e2e = None
     if e2e_steps:
-        runner.capture(concurrency, width, advance=False)
         # Same workload as the device-resident loop: every context starts again at its drawn length (the
         # pool's contents are random either way), so the two numbers differ only by the host round trip.
+        # Each step hands the runner plain host data (request ids, last tokens, lengths, page lists); it packs
+        # them into pinned mirrors, copies ids and lengths and whatever block-table entries changed, replays
+        # the bucket's graph and reads the tokens back.
         grown = 0
-        host_lengths = (contexts + 1).to(torch.int32)
-        host_ids = buffers.output_tokens.cpu()
-        for _ in range(warmup):
-            host_ids, _, _ = runner.step_host(concurrency, host_ids, host_lengths, tables)
-            host_ids = host_ids.clone()
-            host_lengths += 1
+        owners = list(range(concurrency))
+        block_rows = [row[row >= 0].tolist() for row in tables]  # pages reserved for the whole run
+        host_lengths = (contexts + 1).tolist()
+        host_ids = buffers.output_tokens.cpu().tolist()
+        first_h2d = None
+        for _ in range(max(warmup, 1)):
+            host_ids, h2d, _ = runner.decode_rows(owners, host_ids, host_lengths, block_rows)
+            first_h2d = h2d if first_h2d is None else first_h2d
+            host_lengths = [n + 1 for n in host_lengths]
         barrier()
         h2d = d2h = 0
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
-            host_ids, h2d, d2h = runner.step_host(concurrency, host_ids, host_lengths, tables)
-            host_ids = host_ids.clone()
-            host_lengths += 1
+            host_ids, h2d, d2h = runner.decode_rows(owners, host_ids, host_lengths, block_rows)
+            host_lengths = [n + 1 for n in host_lengths]
         torch.cuda.synchronize(device)
         wall = max_over_ranks(time.perf_counter() - t0)
         barrier()
         runner.check_status()
         e2e = {"value": concurrency * e2e_steps / wall, "unit": "tok/s", "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": d2h, "ms_per_step": wall / e2e_steps * 1e3}
-        grown = warmup + e2e_steps
+               "d2h_bytes_per_step": d2h, "ms_per_step": wall / e2e_steps * 1e3,
+               "h2d_bytes_first_step": first_h2d,
+               "note": "block tables are copied when a row changes owner or grows into a page, not every step"}
+        grown = max(warmup, 1) + e2e_steps
+        host_ids = torch.tensor(host_ids, dtype=torch.int64)
 
     # ---- roofline of the dominant kernel: paged decode attention, timed alone with CUDA events ----
     lengths_now = (contexts + 1 + grown).to(torch.int32).to(device)
@@ -650,6 +685,8 @@ def main() -> None:
             if world == 1:
                 cpu_all = cpu_decode_baseline(layer_source=weights.layers[0], embedding=weights.embedding,
                                               final_norm=weights.final_norm)
+            elif launched_with_thread_limit():
+                cpu_all = cpu_baseline_in_clean_process(args)["cpu_baseline"]
             else:  # this rank holds a shard: the baseline runs the unsharded layer, drawn on the CPU
                 cpu_all = cpu_decode_baseline()
             cpu = {k: cpu_all[k] for k in ("value", "unit", "cores", "kind", "sample")}

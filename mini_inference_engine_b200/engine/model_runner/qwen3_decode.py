@@ -324,32 +324,43 @@ class DecodeBuffers:
             raise ValueError("real row counts must agree and fit the graph bucket")
         if self.scratch_pages is None and live < self.batch:
             raise ValueError("padding rows need scratch pages")
-        scratch = set(self.scratch_pages or ())
+        page, width = self.page, self.table_width
+        # Ids and lengths: two vectorised writes into the pinned mirrors.
+        if live:
+            self.host_ids[:live] = torch.as_tensor(ids, dtype=torch.int64)
+            self.host_lengths[:live] = torch.as_tensor(lengths, dtype=torch.int32)
+        if live < self.batch:
+            self.host_ids[live:] = 0
+            self.host_lengths[live:] = 1
+        # Tables: plain Python comparisons per row, tensor writes only for what changed.
+        scratch = None
         dirty: list[tuple[int, int, int]] = []  # (row, first entry, end entry)
-        for row in range(self.batch):
-            if row < live:
-                blocks, length = block_rows[row], int(lengths[row])
-                needed = -(-length // self.page)
-                if length < 1 or len(blocks) > self.table_width or len(blocks) < needed:
-                    raise ValueError("decode position/block row exceeds the fixed graph table capacity")
-                self.host_ids[row], self.host_lengths[row] = int(ids[row]), length
-                same_owner = self._owners[row] is not None and self._owners[row] == owners[row]
-                first = self._held[row] if same_owner else 0
-                if same_owner and len(blocks) < first:
-                    raise ValueError("a request's block list may only grow")
-                if len(blocks) > first:
-                    fresh = [int(b) for b in blocks[first:]]
-                    if any(b < 0 or b in scratch for b in fresh):
-                        raise ValueError("real rows must use valid blocks disjoint from scratch pages")
-                    self.host_tables[row, first:len(blocks)] = torch.tensor(fresh, dtype=torch.int32)
-                    dirty.append((row, first, len(blocks)))
-                self._owners[row], self._held[row] = owners[row], len(blocks)
-            else:
-                self.host_ids[row], self.host_lengths[row] = 0, 1
-                if self._owners[row] is not PADDING:
-                    self.host_tables[row, 0] = self.scratch_pages[row]
-                    dirty.append((row, 0, 1))
-                    self._owners[row], self._held[row] = PADDING, 1
+        owners_now, held = self._owners, self._held
+        for row in range(live):
+            blocks, length = block_rows[row], int(lengths[row])
+            count = len(blocks)
+            if length < 1 or count > width or count * page < length:
+                raise ValueError("decode position/block row exceeds the fixed graph table capacity")
+            previous = owners_now[row]
+            same_owner = previous is not None and previous is not PADDING and previous == owners[row]
+            first = held[row] if same_owner else 0
+            if count == first:
+                continue
+            if count < first:
+                raise ValueError("a request's block list may only grow")
+            fresh = [int(b) for b in blocks[first:]]
+            if scratch is None:
+                scratch = set(self.scratch_pages or ())
+            if min(fresh) < 0 or not scratch.isdisjoint(fresh):
+                raise ValueError("real rows must use valid blocks disjoint from scratch pages")
+            self.host_tables[row, first:count] = torch.tensor(fresh, dtype=torch.int32)
+            dirty.append((row, first, count))
+            owners_now[row], held[row] = owners[row], count
+        for row in range(live, self.batch):
+            if owners_now[row] is not PADDING:
+                self.host_tables[row, 0] = self.scratch_pages[row]
+                dirty.append((row, 0, 1))
+                owners_now[row], held[row] = PADDING, 1
         self.input_ids.copy_(self.host_ids, non_blocking=True)
         self.sequence_lengths.copy_(self.host_lengths, non_blocking=True)
         copied = self.batch * 12
@@ -412,9 +423,12 @@ class MixedBuffers:
     def __init__(self, decode: int, chunk: int, chunks: int, table_width: int, device: torch.device,
                  decode_scratch: tuple[int, ...], chunk_scratch: tuple[int, ...], page: int) -> None:
         self.decode, self.chunk, self.chunks, self.table_width, self.page = decode, chunk, chunks, table_width, page
-        if len(decode_scratch) < decode or len(chunk_scratch) * page < chunk:
+        pad_pages = -(-chunk // page)  # pages the padding tokens of this bucket can spread over
+        if len(decode_scratch) < decode or len(chunk_scratch) < pad_pages:
             raise ValueError("not enough scratch pages for this mixed bucket")
-        self.decode_scratch, self.chunk_scratch = decode_scratch[:decode], chunk_scratch
+        if pad_pages > table_width:
+            raise ValueError(f"a chunk bucket of {chunk} tokens needs block tables at least {pad_pages} pages wide")
+        self.decode_scratch, self.chunk_scratch = decode_scratch[:decode], tuple(chunk_scratch[:pad_pages])
         tokens, rows = decode + chunk, decode + chunks + 1
         self.tokens, self.rows = tokens, rows
         pin = device.type == "cuda"
