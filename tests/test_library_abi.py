@@ -57,3 +57,15 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_lib, "LIB_PATH", tmp_path / "libmie_b200.so")
     with pytest.raises(_lib.MieLibraryError, match="no CPU or PyTorch fallback"):
         _lib.load()
+
+
+def test_library_path_override(monkeypatch, tmp_path):
+    """``MIE_LIBRARY_PATH`` points the binding at a build kept elsewhere; a wrong path fails as loudly."""
+
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setenv("MIE_LIBRARY_PATH", str(build.LIB_PATH))
+    assert _lib.library_path() == build.LIB_PATH and _lib.load().mie_version() >= 1
+    monkeypatch.setattr(_lib, "_lib", None)
+    monkeypatch.setenv("MIE_LIBRARY_PATH", str(tmp_path / "elsewhere.so"))
+    with pytest.raises(_lib.MieLibraryError, match="elsewhere.so is missing"):
+        _lib.load()
