@@ -504,6 +504,18 @@ def main() -> None:
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     group = None
+    early_cpu = None
+    if world > 1 and rank == 0 and not args.no_cpu_baseline and not args.breakdown:
+        # The CPU baseline of a multi-rank run is taken FIRST, while the other ranks block (without spinning)
+        # in the rendezvous below: ranks that wait for rank 0 inside a collective poll on the host and take the
+        # cores the baseline needs (measured: 16 s per layer instead of 0.1 s).
+        try:
+            base = (cpu_baseline_in_clean_process(args)["cpu_baseline"] if launched_with_thread_limit()
+                    else cpu_decode_baseline())
+            early_cpu = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        except Exception as error:  # the baseline is reported, never required
+            early_cpu = {"value": None, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"failed: {error!r}"}
     if world > 1:
         # No NVLink multicast (NVLS) objects: a rank that leaves while its memory is bound to one can raise
         # NVLink faults on its peers, and the exchange kernels of this library use plain peer loads anyway.
@@ -678,17 +690,12 @@ def main() -> None:
         torch.distributed.all_gather_into_tensor(gathered, mine)
         tokens_agree = bool((gathered == gathered[0:1]).all().item())
 
-    cpu = None
-    if rank == 0 and not args.no_cpu_baseline:
+    cpu = early_cpu
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
         use_all_host_cores()
         try:
-            if world == 1:
-                cpu_all = cpu_decode_baseline(layer_source=weights.layers[0], embedding=weights.embedding,
-                                              final_norm=weights.final_norm)
-            elif launched_with_thread_limit():
-                cpu_all = cpu_baseline_in_clean_process(args)["cpu_baseline"]
-            else:  # this rank holds a shard: the baseline runs the unsharded layer, drawn on the CPU
-                cpu_all = cpu_decode_baseline()
+            cpu_all = cpu_decode_baseline(layer_source=weights.layers[0], embedding=weights.embedding,
+                                          final_norm=weights.final_norm)
             cpu = {k: cpu_all[k] for k in ("value", "unit", "cores", "kind", "sample")}
         except Exception as error:  # the baseline is reported, never required
             cpu = {"value": None, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",

@@ -103,7 +103,8 @@ __device__ __forceinline__ long long block_sum_ll(long long v, long long* smem) 
 //     ceil(items / warps) x (time of one chunk + what a warp loses between two items),
 // with items = kv_heads x sum_b ceil(length_b / chunk).  Policy 1 evaluates that with the batch's real
 // lengths for a grid of chunk sizes and takes the cheapest: a chunk size that just misses a whole number of
-// rounds costs a full extra round on a few warps.  `switch_tokens` is the between-items loss (queue pop,
+// rounds costs a full extra round on a few warps (see the limit below for where this applies).
+// `switch_tokens` is the between-items loss (queue pop,
 // metadata, refilling the TMA ring, writing and later merging a partial) expressed in tokens of streaming;
 // 128 tokens of one bf16 KV head (64 KB) reproduces the measured ranking of chunk sizes on an 8-way
 // head shard (384 and 1024 tokens best, 512 and 192 worst).
@@ -118,7 +119,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
   __shared__ int warp_tot[32];
   __shared__ int cand_part[32][kPlanCands];
   __shared__ int cand_count[kPlanCands];
-  __shared__ int running_s, running_r;
+  __shared__ int running_s;
   __shared__ long long chunk_s;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   chain_wait();
@@ -156,9 +157,19 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
     }
     __syncthreads();
     if (tid == 0) {
-      long long best = kPlanChunks[kPlanCands - 1];
+      // With several KV heads per rank and enough work for four items of at least 512 tokens per warp the kernel is bound by
+      // HBM, not by the queue's rounds, and finer items measured better (C=256 at 1 / 2 ranks): there the
+      // chunk stays at or below the four-items-per-warp size.  A single KV head per rank, or a batch too
+      // small for that, is where whole rounds decide.
+      long long limit = kMaxChunk;
+      if (kv_heads >= 2) {
+        const long long four = align_up((total * kv_heads + 4ll * warps - 1) / (4ll * warps), kTileTokens);
+        if (four >= 512) limit = four;
+      }
+      long long best = kPlanChunks[0];
       long long best_cost = -1;
       for (int j = kPlanCands - 1; j >= 0; --j) {  // larger chunks first: they win ties (fewer partials)
+        if (kPlanChunks[j] > limit && j > 0) continue;
         if (cand_count[j] > sc.cap) continue;      // more (request, chunk) pairs than the scratch holds
         const long long items = (long long)cand_count[j] * kv_heads;
         const long long rounds = (items + warps - 1) / warps;
@@ -180,8 +191,10 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
     chunk = align_up((total + room - 1) / room, kTileTokens);  // still exact, only coarser
   }
 
-  // Pass 1: offsets[b] = first (request, chunk) pair of request b (the rows of its partial results).
-  if (tid == 0) running_s = running_r = 0;
+  // Work list in request order, a request's chunks next to each other (queueing the full-sized chunks of
+  // all requests first and the shorter last chunks at the end was measured 2 % slower at the same chunk size:
+  // neighbouring items then no longer read neighbouring pages).
+  if (tid == 0) running_s = 0;
   __syncthreads();
   for (int base = 0; base < batch; base += blockDim.x) {
     const int b = base + tid;
@@ -200,7 +213,14 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
     __syncthreads();
     int before = running_s;
     for (int w = 0; w < warp; ++w) before += warp_tot[w];
-    if (b < batch) sc.offsets[b] = before + incl - c;
+    const int excl = before + incl - c;
+    if (b < batch) {
+      sc.offsets[b] = excl;
+      for (int j = 0; j < c; ++j) {
+        sc.item_seq[excl + j] = b;
+        sc.item_chunk[excl + j] = j;
+      }
+    }
     __syncthreads();
     if (tid == 0) {
       int t = 0;
@@ -210,52 +230,6 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
     __syncthreads();
   }
   const int pairs = running_s;
-  // Requests that have at least one chunk.
-  int live_local = 0;
-  for (int b = tid; b < batch; b += blockDim.x) {
-    live_local += read_length(lengths, positions, b, capacity_tokens, nullptr) > 0 ? 1 : 0;
-  }
-  const int live = (int)block_sum_ll(live_local, red);
-
-  // Pass 2: the work list.  Every chunk but a request's last is full-sized; those come first (in request
-  // order), the last chunks - mostly partial, so shorter - after them, so that the queue ends on its
-  // smallest items.
-  for (int base = 0; base < batch; base += blockDim.x) {
-    const int b = base + tid;
-    int c = 0;
-    if (b < batch) {
-      const long long rl = read_length(lengths, positions, b, capacity_tokens, nullptr);
-      c = (int)((rl + chunk - 1) / chunk);
-    }
-    const int flag = c > 0 ? 1 : 0;
-    int incl = flag;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int n = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += n;
-    }
-    if (lane == 31) warp_tot[warp] = incl;
-    __syncthreads();
-    int before = running_r;
-    for (int w = 0; w < warp; ++w) before += warp_tot[w];
-    const int rank = before + incl - flag;  // requests with chunks in front of b
-    if (b < batch && c > 0) {
-      const int first = sc.offsets[b] - rank;  // full-sized chunks in front of b
-      for (int j = 0; j + 1 < c; ++j) {
-        sc.item_seq[first + j] = b;
-        sc.item_chunk[first + j] = j;
-      }
-      sc.item_seq[pairs - live + rank] = b;
-      sc.item_chunk[pairs - live + rank] = c - 1;
-    }
-    __syncthreads();
-    if (tid == 0) {
-      int t = 0;
-      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += warp_tot[w];
-      running_r += t;
-    }
-    __syncthreads();
-  }
   if (tid == 0) {
     sc.offsets[batch] = pairs;
     sc.header[0] = (int)(chunk > 0x7fffffffll ? 0x7fffffff : chunk);
