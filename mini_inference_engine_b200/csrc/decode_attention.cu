@@ -748,12 +748,16 @@ __global__ void __launch_bounds__(kWarps8 * 32, 1)
         vref = vref_new;
         const uint32_t pa0 = Mma16816<__half>::pack(p0 * (vs[0] * lift), p1 * (vs[1] * lift));
         const uint32_t pa2 = Mma16816<__half>::pack(p2 * (vs[2] * lift), p3 * (vs[3] * lift));
+        // Most tiles move neither the running maximum nor the V-scale reference of any head: then the
+        // 32 multiplications by 1 are skipped (this kernel is bound by instruction issue, not by memory).
+        if (__any_sync(0xffffffffu, rescale != 1.f)) {
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          oe[c][0] *= rescale;
-          oe[c][1] *= rescale;
-          oo[c][0] *= rescale;
-          oo[c][1] *= rescale;
+          for (int c = 0; c < 8; ++c) {
+            oe[c][0] *= rescale;
+            oe[c][1] *= rescale;
+            oo[c][0] *= rescale;
+            oo[c][1] *= rescale;
+          }
         }
         // O += P' V8
 #pragma unroll
