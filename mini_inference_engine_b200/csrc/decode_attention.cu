@@ -109,8 +109,12 @@ __device__ __forceinline__ long long block_sum_ll(long long v, long long* smem) 
 // 128 tokens of one bf16 KV head (64 KB) reproduces the measured ranking of chunk sizes on an 8-way
 // head shard (384 and 1024 tokens best, 512 and 192 worst).
 constexpr int kPlanCands = 21;
-__constant__ int kPlanChunks[kPlanCands] = {64,  80,  96,  112, 128, 160, 192,  224,  256,  320, 384,
-                                            448, 512, 640, 768, 896, 1024, 1280, 1536, 1792, 2048};
+// Candidate j (compile-time in the unrolled loops, so the divisions below are by constants).
+__host__ __device__ constexpr int plan_chunk(int j) {
+  constexpr int table[kPlanCands] = {64,  80,  96,  112, 128, 160, 192,  224,  256,  320, 384,
+                                     448, 512, 640, 768, 896, 1024, 1280, 1536, 1792, 2048};
+  return table[j];
+}
 
 __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, IndexView positions, int batch,
                                                             long long capacity_tokens, int kv_heads, int policy,
@@ -125,8 +129,15 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
   chain_wait();
   chain_release();
 
-  long long local = 0;
-  for (int b = tid; b < batch; b += blockDim.x) local += read_length(lengths, positions, b, capacity_tokens, status);
+  // With one thread per request (the usual launch) a request's length is read once and kept.
+  const bool one_each = batch <= (int)blockDim.x;
+  long long own = 0, local = 0;
+  if (one_each) {
+    if (tid < batch) own = read_length(lengths, positions, tid, capacity_tokens, status);
+    local = own;
+  } else {
+    for (int b = tid; b < batch; b += blockDim.x) local += read_length(lengths, positions, b, capacity_tokens, status);
+  }
   const long long total = block_sum_ll(local, red);
   const long long room = sc.cap - batch;  // > 0, checked on the host
 
@@ -138,9 +149,9 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
 #pragma unroll
     for (int j = 0; j < kPlanCands; ++j) mine[j] = 0;
     for (int b = tid; b < batch; b += blockDim.x) {
-      const int rl = (int)read_length(lengths, positions, b, capacity_tokens, nullptr);
+      const int rl = (int)(one_each ? own : read_length(lengths, positions, b, capacity_tokens, nullptr));
 #pragma unroll
-      for (int j = 0; j < kPlanCands; ++j) mine[j] += (rl + kPlanChunks[j] - 1) / kPlanChunks[j];
+      for (int j = 0; j < kPlanCands; ++j) mine[j] += (rl + plan_chunk(j) - 1) / plan_chunk(j);
     }
 #pragma unroll
     for (int j = 0; j < kPlanCands; ++j) {
@@ -166,17 +177,18 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
         const long long four = align_up((total * kv_heads + 4ll * warps - 1) / (4ll * warps), kTileTokens);
         if (four >= 512) limit = four;
       }
-      long long best = kPlanChunks[0];
+      long long best = plan_chunk(0);
       long long best_cost = -1;
+#pragma unroll
       for (int j = kPlanCands - 1; j >= 0; --j) {  // larger chunks first: they win ties (fewer partials)
-        if (kPlanChunks[j] > limit && j > 0) continue;
+        if (plan_chunk(j) > limit && j > 0) continue;
         if (cand_count[j] > sc.cap) continue;      // more (request, chunk) pairs than the scratch holds
         const long long items = (long long)cand_count[j] * kv_heads;
         const long long rounds = (items + warps - 1) / warps;
-        const long long cost = rounds * (kPlanChunks[j] + switch_tokens);
+        const long long cost = rounds * (plan_chunk(j) + switch_tokens);
         if (best_cost < 0 || cost < best_cost) {
           best_cost = cost;
-          best = kPlanChunks[j];
+          best = plan_chunk(j);
         }
       }
       chunk_s = best;
@@ -200,7 +212,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_kernel(IndexView lengths, I
     const int b = base + tid;
     int c = 0;
     if (b < batch) {
-      const long long rl = read_length(lengths, positions, b, capacity_tokens, nullptr);
+      const long long rl = one_each ? own : read_length(lengths, positions, b, capacity_tokens, nullptr);
       c = (int)((rl + chunk - 1) / chunk);
     }
     int incl = c;
@@ -1076,6 +1088,13 @@ long long per_chunk_bytes(int q_heads, int head_dim) { return 8 + (long long)q_h
 
 // (request, chunk) pairs `mie_decode_scratch_bytes` makes room for beyond one per request: four items per
 // warp.  The plan kernel considers more items per warp only while they fit the scratch it was given.
+// One thread per request, at least two warps, at most the kernel's bound: a small batch does not pay for
+// block-wide reductions over 32 warps.
+int plan_threads(int batch) {
+  const int threads = (batch + 31) / 32 * 32;
+  return threads < 64 ? 64 : threads > kPlanThreads ? kPlanThreads : threads;
+}
+
 int target_seq_chunks(int kv_heads) {
   const int items = sm_count() * kWarps * 4;
   return (items + kv_heads - 1) / kv_heads;
@@ -1217,7 +1236,7 @@ extern "C" int mie_paged_decode_attention(mie_view4_t query, mie_view4_t out, mi
                  table_width, scale * 1.4426950408889634f, plan_slot, status, reinterpret_cast<uint8_t*>(out_q8), ldq8,
                  out_scales, out_scale_ld, 0};
   if (!use_plan) {
-    plan_kernel<<<1, kPlanThreads, 0, stream>>>(p.lengths, p.positions, batch, (long long)table_width * block_size,
+    plan_kernel<<<1, plan_threads(batch), 0, stream>>>(p.lengths, p.positions, batch, (long long)table_width * block_size,
                                                 kv_heads, split_policy, sm_count() * kWarps, 128, sc, status);
     MIE_LAUNCH_CHECK("plan_kernel");
   }
@@ -1352,7 +1371,7 @@ extern "C" int mie_paged_decode_attention_kv8(mie_view4_t query, mie_view4_t out
                  table_width, scale * 1.4426950408889634f, plan_slot, status, reinterpret_cast<uint8_t*>(out_q8), ldq8,
                  out_scales, out_scale_ld, 0};
   if (!use_plan) {
-    plan_kernel<<<1, kPlanThreads, 0, stream>>>(p.lengths, p.positions, batch, (long long)table_width * kTileTokens,
+    plan_kernel<<<1, plan_threads(batch), 0, stream>>>(p.lengths, p.positions, batch, (long long)table_width * kTileTokens,
                                                 kv_heads, split_policy, sm_count() * kWarps8, 256, sc, status);
     MIE_LAUNCH_CHECK("plan_kernel");
   }
