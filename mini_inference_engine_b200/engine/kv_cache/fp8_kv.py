@@ -49,6 +49,19 @@ class Fp8KvPool:
             self.scales[layer, :, :, which].copy_(scales)
 
 
+    def dequantized_pages(self, layer: int, page_ids: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+        """The pages ``page_ids`` (int64, on the pool's device) of layer ``layer`` as two contiguous bf16 tensors
+        ``[len(page_ids), kv_heads, 16, 128]``: ``e4m3 * scale`` rounded to bf16, what a reader of the cache sees.
+        The prompt-chunk attention kernel reads bf16 pages, so a chunk step stages its requests' pages this way."""
+
+        staged = []
+        for which in (0, 1):
+            data = self.data[layer, :, :, which].index_select(0, page_ids)
+            scales = self.scales[layer, :, :, which].index_select(0, page_ids)
+            staged.append((data.view(torch.float8_e4m3fn).float() * scales.unsqueeze(-1)).to(torch.bfloat16))
+        return staged[0], staged[1]
+
+
 def quantize_kv_rows(rows: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """``[..., 128]`` bf16/fp16 rows -> (e4m3 bytes as uint8, fp32 scales ``[...]``), with torch ops on the
     rows' device.  The CUDA writer (``mie_qkv_norm_rope_write_kv8``) produces the same bits."""

@@ -552,8 +552,8 @@ class Qwen3DecodeRunner:
         self.kv_dtype = kv_dtype
         self.kv8 = None
         if kv_dtype == "fp8":
-            # Opt-in e4m3 K/V pool (one fp32 scale per token and KV head): decode steps only - the prompt
-            # kernels read bf16 pages.  bf16 stays the default and the parity path.
+            # Opt-in e4m3 K/V pool (one fp32 scale per token and KV head).  Decode rows read it directly;
+            # prompt chunks attend bf16 staging copies of their pages.  bf16 stays the default and the parity path.
             if shape.page != 16 or shape.head_dim != 128:
                 raise ValueError("the FP8 KV cache needs 16-token pages and head_dim 128")
             self.kv8 = Fp8KvPool(layers, self.total_pages, self.local_kv_heads, self.device)
@@ -778,9 +778,6 @@ class Qwen3DecodeRunner:
         all other operators run once over the whole stream.  ``logit_rows`` selects the rows that are
         projected to logits; their greedy tokens are returned in that order."""
 
-        if self.kv8 is not None:
-            raise NotImplementedError("prompt chunks over the FP8 KV cache are not built: the prefill kernel reads "
-                                      "bf16 pages (kv_dtype='fp8' serves decode steps only)")
         shape, lib = self.shape, _lib.load()
         stream = _lib.stream_arg(self.device)
         tokens = int(input_ids.shape[0])
@@ -796,13 +793,29 @@ class Qwen3DecodeRunner:
         # buffers, NCCL all-reduce + the norm kernel otherwise).
         _, _, quantized = self._norm(hidden, layers[0].input_norm, quantize=True)
         residual, normed = hidden, None
+        chunk_tables = block_tables[decode_rows:]
+        if self.kv8 is not None and chunk_tokens:
+            # The chunk kernel reads bf16 pages: per layer, after the writer has quantised the new rows into the
+            # FP8 pool, the chunk requests' pages (cached prefix and the chunk itself) are dequantised into a
+            # staging set of bf16 pages addressed by a renumbered table, so a chunk attends exactly what the
+            # cache holds, as the decode steps after it will.
+            staged_ids = chunk_tables.clamp_min(0).flatten().long()
+            numbering = torch.arange(staged_ids.numel(), dtype=chunk_tables.dtype, device=self.device)
+            chunk_tables = torch.where(chunk_tables >= 0, numbering.view_as(chunk_tables),
+                                       torch.full_like(chunk_tables, -1))
         for index, layer in enumerate(layers):
             qkv = self._gemm(quantized, layer.qkv, layer.qkv_scale, tokens, shape.hidden)
             queries = torch.empty(tokens, lq, hd, dtype=torch.bfloat16, device=self.device)
             self._qkv_post(index, layer, qkv, queries, token_positions, token_to_sequence, block_tables, tokens,
                            table_rows)
             attended = torch.empty_like(queries)
-            if decode_rows:
+            if decode_rows and self.kv8 is not None:
+                launch_decode_attention_kv8(queries[:decode_rows].unsqueeze(2), attended[:decode_rows].unsqueeze(2),
+                                            self.kv8.data[index], self.kv8.scales[index], block_tables[:decode_rows],
+                                            decode_lengths, None, scale=scale, scratch=self.scratch, split_policy=1,
+                                            use_plan=index % PLAN_SLOTS != 0, plan_slot=index % PLAN_SLOTS,
+                                            status=self.status)
+            elif decode_rows:
                 launch_decode_attention(queries[:decode_rows].unsqueeze(2), attended[:decode_rows].unsqueeze(2),
                                         self.key_blocks[index], self.value_blocks[index],
                                         block_tables[:decode_rows], decode_lengths, None, scale=scale,
@@ -810,9 +823,13 @@ class Qwen3DecodeRunner:
                                         split_policy=1, use_plan=index % PLAN_SLOTS != 0,
                                         plan_slot=index % PLAN_SLOTS, status=self.status)
             if chunk_tokens:
-                launch_flash_prefill(queries[decode_rows:], attended[decode_rows:], self.key_blocks[index],
-                                     self.value_blocks[index], block_tables[decode_rows:], cu_seqlens, kv_lens,
-                                     max_query_len=max_query_len, scale=scale, status=self.status)
+                if self.kv8 is not None:
+                    key_pages, value_pages = self.kv8.dequantized_pages(index, staged_ids)
+                else:
+                    key_pages, value_pages = self.key_blocks[index], self.value_blocks[index]
+                launch_flash_prefill(queries[decode_rows:], attended[decode_rows:], key_pages, value_pages,
+                                     chunk_tables, cu_seqlens, kv_lens, max_query_len=max_query_len, scale=scale,
+                                     status=self.status)
             attn_q = self._quantize(attended.view(tokens, lq * hd))
             _, residual, quantized = self._row_parallel_then_norm(attn_q, layer.o, layer.o_scale, tokens, lq * hd,
                                                                   residual, layer.post_norm, quantize=True)

@@ -71,11 +71,12 @@ def decode_step(weights, key_blocks, value_blocks, input_ids, sequence_lengths, 
 
 
 def prefill_step(weights, key_blocks, value_blocks, input_ids, token_to_sequence, token_positions, block_tables,
-                 cu_seqlens, kv_lens, *, q_heads, kv_heads, head_dim, eps, theta, return_hidden=False):
+                 cu_seqlens, kv_lens, *, q_heads, kv_heads, head_dim, eps, theta, return_hidden=False, kv_image=None):
     """Packed prompt chunks through the model (engine/model_runner/qwen3_packed.py:29-113; attention adapter
     packed branch engine/kv_cache/qwen3_paged.py:102-189): per layer the new K/V rows are scattered to their
     pages, attention is causal within a chunk over the whole cached prefix, and each request's last row is
-    projected to logits.  Returns the greedy next token of every request."""
+    projected to logits.  Returns the greedy next token of every request.  ``kv_image``: as in
+    ``decode_step`` (the chunk then attends what an FP8 cache holds of its own rows too)."""
 
     tokens = input_ids.shape[0]
     hidden = weights.embedding.index_select(0, input_ids)
@@ -90,6 +91,8 @@ def prefill_step(weights, key_blocks, value_blocks, input_ids, token_to_sequence
         k = hot_path.rms_norm(k.reshape(1, tokens, kv_heads, head_dim), layer.k_norm, eps).transpose(1, 2)
         v = v.reshape(1, tokens, kv_heads, head_dim).transpose(1, 2)
         q, k = hot_path.apply_rotary_pos_emb(q, k, cos, sin)
+        if kv_image is not None:
+            k, v = kv_image(k), kv_image(v)
         hot_path.write_packed_kv(k, v, token_to_sequence, token_positions, block_tables, key_blocks[index],
                                  value_blocks[index])
         attended = hot_path.chunked_prefill_attention(q[0].transpose(0, 1).contiguous(), key_blocks[index],

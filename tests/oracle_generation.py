@@ -7,10 +7,11 @@ import torch
 from oracle import qwen3_model
 
 
-def oracle_generate(cpu_weights, shape, prompt, new_tokens: int):
+def oracle_generate(cpu_weights, shape, prompt, new_tokens: int, kv_image=None):
     """Whole-prompt prefill then ``new_tokens - 1`` decode steps of ONE request on a private page pool.
     Returns ``(tokens, margin)``: ``margin`` is the smallest, over the steps, of the oracle's top-2 logit gap
-    divided by the magnitude of its top logit - how decisively the oracle's own arithmetic picks each token."""
+    divided by the magnitude of its top logit - how decisively the oracle's own arithmetic picks each token.
+    ``kv_image`` is handed to both oracle steps (an FP8 KV cache: quantise -> dequantise of every stored row)."""
 
     page = shape.page
     pages = -(-(len(prompt) + new_tokens) // page)
@@ -20,7 +21,7 @@ def oracle_generate(cpu_weights, shape, prompt, new_tokens: int):
     tables = torch.arange(pages, dtype=torch.int32).view(1, pages)
     n = len(prompt)
     kwargs = dict(q_heads=shape.q_heads, kv_heads=shape.kv_heads, head_dim=shape.head_dim, eps=shape.rms_eps,
-                  theta=shape.rope_theta, return_hidden=True)
+                  theta=shape.rope_theta, return_hidden=True, kv_image=kv_image)
     picked, _, logits = qwen3_model.prefill_step(
         cpu_weights, keys, values, torch.tensor(prompt), torch.zeros(n, dtype=torch.int32),
         torch.arange(n, dtype=torch.int32), tables, torch.tensor([0, n], dtype=torch.int32),

@@ -215,8 +215,91 @@ def test_decode_step_over_the_fp8_cache(device):
     # The same rows through a bucket graph give the same tokens.
     tokens, _, _ = runner.decode_rows(["a", "b", "c"], ids, lengths, blocks)
     assert tokens == got.tolist()
-    with pytest.raises(NotImplementedError, match="decode steps only"):
-        runner.prefill_forward(torch.tensor(ids, device=device), torch.zeros(3, dtype=torch.int32, device=device),
-                               torch.arange(3, dtype=torch.int32, device=device), tables.to(device),
-                               torch.tensor([0, 3], dtype=torch.int32, device=device),
-                               torch.tensor([3], dtype=torch.int32, device=device), 3)
+
+
+def _image(rows):
+    return hot_path.dequantize_kv_rows(*hot_path.quantize_kv_rows(rows))
+
+
+def test_prompt_chunks_over_the_fp8_cache(device):
+    """A prompt in two chunks (the second over a cached prefix) next to a whole prompt: the writer quantises
+    the new rows, the chunk kernel attends the dequantised pages.  Against the oracle's packed step whose
+    stored rows go through the same quantise -> dequantise image."""
+
+    from mini_inference_engine_b200.engine.model_runner.qwen3_decode import Qwen3DecodeRunner, Qwen3Shape, Qwen3Weights
+    from oracle import qwen3_model
+
+    shape = Qwen3Shape(layers=2, hidden=512, q_heads=4, kv_heads=2, head_dim=128, intermediate=1024, vocab=2048)
+    cpu = Qwen3Weights(shape, torch.device("cpu"), seed=36)
+    runner = Qwen3DecodeRunner(cpu.to(device), num_pages=24, max_batch=4, max_context=128, kv_dtype="fp8")
+    generator = torch.Generator().manual_seed(4)
+    prompt_a = torch.randint(0, shape.vocab, (45,), generator=generator)
+    prompt_b = torch.randint(0, shape.vocab, (19,), generator=generator)
+    blocks = [[5, 2, 9], [7, 1]]
+    tables = torch.full((2, runner.table_width), -1, dtype=torch.int32)
+    for row, page_ids in enumerate(blocks):
+        tables[row, :len(page_ids)] = torch.tensor(page_ids, dtype=torch.int32)
+    keys = torch.zeros(2, runner.total_pages, 2, 16, 128, dtype=torch.bfloat16)
+    values = torch.zeros_like(keys)
+    kwargs = dict(q_heads=4, kv_heads=2, head_dim=128, eps=shape.rms_eps, theta=shape.rope_theta, return_hidden=True,
+                  kv_image=_image)
+    # step 1: the first 30 tokens of A; step 2: the last 15 of A (prefix 30) packed with all of B
+    steps = [
+        (prompt_a[:30], [0] * 30, list(range(30)), [0, 30], [30]),
+        (torch.cat([prompt_a[30:], prompt_b]), [0] * 15 + [1] * 19, list(range(30, 45)) + list(range(19)),
+         [0, 15, 34], [45, 19]),
+    ]
+    for ids, owners, positions, cu, kv in steps:
+        meta = [torch.tensor(x, dtype=torch.int32) for x in (owners, positions, cu, kv)]
+        expected, _, want = qwen3_model.prefill_step(cpu, keys, values, ids, meta[0], meta[1], tables, meta[2],
+                                                     meta[3], **kwargs)
+        got, logits = runner.prefill_forward(ids.to(device), meta[0].to(device), meta[1].to(device),
+                                             tables.to(device), meta[2].to(device), meta[3].to(device),
+                                             max(b - a for a, b in zip(cu, cu[1:])), return_logits=True)
+        runner.check_status()
+        want = want.float()
+        assert (logits.cpu().float() - want).abs().max().item() <= 0.08 * want.abs().max().item()
+        top2 = want.topk(2, dim=-1).values
+        for row in range(len(kv)):
+            if (top2[row, 0] - top2[row, 1]) > 0.1 * top2[row, 0].abs():
+                assert int(got[row]) == int(expected[row])
+    # Layer 0 sees the same inputs on both sides, so its cache rows are the oracle's rows quantised, bit for bit
+    # (the oracle's pool holds the bf16 image; quantising an image again reproduces its bytes and scales).
+    for row, length in ((0, 45), (1, 19)):
+        for position in (0, 15, 16, length - 1):
+            page, slot = blocks[row][position // 16], position % 16
+            for which, pool in enumerate((keys, values)):
+                want_q, want_s = hot_path.quantize_kv_rows(pool[0, page, :, slot])
+                assert torch.equal(runner.kv8.scales[0, page, :, which, slot].cpu(), want_s)
+                assert torch.equal(runner.kv8.data[0, page, :, which, slot].cpu(), want_q)
+
+
+@pytest.mark.parametrize("mixed", [False, True])
+def test_generation_over_the_fp8_cache_equals_the_oracle(mixed, device):
+    """Continuous batching with ``kv_dtype="fp8"`` (chunked prompts, bucket graphs, and with ``mixed`` the captured
+    prefill + decode steps) against the oracle generating over the quantise -> dequantise image of its cache.
+    Seeds chosen so that the oracle's top-2 gap is at least 10 % of its top logit at every step (re-checked
+    here): outside the noise of e4m3 rows, so the tokens are compared with ``==``."""
+
+    from mini_inference_engine_b200.engine.model_runner.continuous import ContinuousBatcher
+    from mini_inference_engine_b200.engine.model_runner.qwen3_decode import Qwen3DecodeRunner, Qwen3Shape, Qwen3Weights
+    from oracle_generation import oracle_generate
+
+    shape = Qwen3Shape(layers=2, hidden=512, q_heads=4, kv_heads=2, head_dim=128, intermediate=1024, vocab=2048)
+    cpu = Qwen3Weights(shape, torch.device("cpu"), seed=33)
+    generator = torch.Generator().manual_seed(0)
+    requests = [(f"r{i}", torch.randint(0, shape.vocab, (n,), generator=generator).tolist(), new)
+                for i, (n, new) in enumerate([(37, 4), (150, 8), (20, 12)])]
+    expected = {}
+    for rid, prompt, new in requests:
+        expected[rid], margin = oracle_generate(cpu, shape, prompt, new, kv_image=_image)
+        assert margin >= 0.1, f"the oracle itself is not decisive for {rid}: margin {margin:.4f}"
+    runner = Qwen3DecodeRunner(cpu.to(device), num_pages=48, max_batch=4, max_context=256, max_chunks=4,
+                               chunk_buckets=(128,), kv_dtype="fp8")
+    batcher = ContinuousBatcher(runner, max_prefill_tokens=128, mixed=mixed)
+    for rid, prompt, new in requests:
+        batcher.submit(rid, prompt, new)
+    results = batcher.run()
+    assert int(runner.status.item()) == 0
+    for rid, _, _ in requests:
+        assert results[rid] == expected[rid], rid
