@@ -469,45 +469,6 @@ int mie_tp_reduce_rms_norm(const mie_tp_peers_t* peers, int32_t tp, int32_t rank
                            int32_t rows, int32_t cols, float eps, uint32_t* state, uint32_t max_polls,
                            int32_t* status, void* stream);
 
-/*
- * The same exchange with the reduce-scatter half moved into the projection:
- * mie_fp8_gemm_tp_push is mie_fp8_gemm for a row-parallel projection (bf16
- * output) whose epilogue stores every finished output row straight into the
- * memory of the rank that owns it in the exchange (plain peer stores, no
- * multimem, no TMA on peer memory) instead of a local y: row t goes to
- * rows[t / rows_per_rank] + t * ld.  A rank therefore passes, for every
- * owner o, the address of ITS OWN slot in o's landing area.  After its stores
- * each CTA publishes them with a system-scope fence and adds the number of
- * elements it delivered to arrived[t / rows_per_rank] (red.release.sys), so
- * the transfer of a tile overlaps the tiles still being computed and no
- * "partials complete" round trip is needed.
- *
- * mie_tp_reduce_rms_norm_pushed then needs no peer loads: landing is this
- * rank's LOCAL landing area, slot s (rank s's partial rows, [rows, ld_landing]
- * bf16 indexed by the global row) at landing + s * slot_stride elements, and
- * arrived its local counter (zeroed once, never reset: the kernel keeps the
- * running total in state[3]).  It waits until tp * owned rows * cols
- * elements have arrived since the previous call and continues exactly like
- * mie_tp_reduce_rms_norm (same sums in the same rank order: same bits).
- * rows_per_rank must be ceil(rows / tp) for the rows of the call that follows.
- */
-typedef struct {
-  void* rows[MIE_TP_MAX_RANKS];        /* owner o: this rank's slot in o's landing area */
-  uint32_t* arrived[MIE_TP_MAX_RANKS]; /* owner o: o's arrival counter */
-  int64_t ld;                          /* elements between landing rows (>= n, multiple of 8) */
-  int32_t tp, rows_per_rank;
-} mie_tp_push_t;
-
-int mie_fp8_gemm_tp_push(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
-                         int64_t ldw, const float* w_scale, int32_t w_scale_ld, const mie_tp_push_t* push, int32_t m,
-                         int32_t n, int32_t k, int32_t max_split, int32_t flags, int32_t* status, void* stream);
-
-int mie_tp_reduce_rms_norm_pushed(const mie_tp_peers_t* peers, int32_t tp, int32_t rank, const void* landing,
-                                  int64_t ld_landing, int64_t slot_stride, const uint32_t* arrived,
-                                  const void* residual, void* summed, const void* weight, int64_t ldq,
-                                  int32_t scale_ld, int32_t rows, int32_t cols, float eps, uint32_t* state,
-                                  uint32_t max_polls, int32_t* status, void* stream);
-
 #ifdef __cplusplus
 }
 #endif

@@ -64,13 +64,6 @@ class TpPeersT(ctypes.Structure):
                 ("flags", c_void_p * TP_MAX_RANKS)]
 
 
-class TpPushT(ctypes.Structure):
-    """``mie_tp_push_t``: where a row-parallel projection delivers its rows under tensor parallelism."""
-
-    _fields_ = [("rows", c_void_p * TP_MAX_RANKS), ("arrived", c_void_p * TP_MAX_RANKS), ("ld", c_int64),
-                ("tp", c_int32), ("rows_per_rank", c_int32)]
-
-
 _SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "mie_last_error": (c_char_p, []),
     "mie_version": (ctypes.c_int, []),
@@ -132,13 +125,6 @@ _SIGNATURES: dict[str, tuple[object, list[object]]] = {
     "mie_tp_reduce_rms_norm": (ctypes.c_int, [ctypes.POINTER(TpPeersT), c_int32, c_int32, c_int64, c_void_p, c_void_p,
                                               c_void_p, c_int64, c_int32, c_int32, c_int32, c_float, c_void_p,
                                               ctypes.c_uint32, c_void_p, c_void_p]),
-    "mie_fp8_gemm_tp_push": (ctypes.c_int, [c_void_p, c_int64, c_void_p, c_int32, c_void_p, c_int64, c_void_p, c_int32,
-                                            ctypes.POINTER(TpPushT), c_int32, c_int32, c_int32, c_int32, c_int32,
-                                            c_void_p, c_void_p]),
-    "mie_tp_reduce_rms_norm_pushed": (ctypes.c_int, [ctypes.POINTER(TpPeersT), c_int32, c_int32, c_void_p, c_int64,
-                                                     c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
-                                                     c_int32, c_int32, c_int32, c_float, c_void_p, ctypes.c_uint32,
-                                                     c_void_p, c_void_p]),
 }
 
 _lib: ctypes.CDLL | None = None

@@ -60,12 +60,6 @@ struct GemmParams {
   // wait is taken at the end of the kernel instead of the start (second launch of a two-launch GEMM, whose
   // inputs are already known to be complete because the first launch waited for them).
   int tile_begin, tile_end, late_wait;
-  // Tensor-parallel push (push_tp > 0): output row t does not go to y but to the rank that owns it in the
-  // exchange that follows, owner = t / push_rows, at push_dst[owner] + t * ldy (peer memory, plain stores);
-  // after its stores a CTA adds the number of elements it delivered to push_arrived[owner].
-  int push_tp, push_rows;
-  uint16_t* push_dst[MIE_TP_MAX_RANKS];
-  unsigned* push_arrived[MIE_TP_MAX_RANKS];
 };
 
 // Scale staging: per chunk of kChunkKb K blocks the promotion warps pull every
@@ -106,34 +100,11 @@ constexpr int max_reduction_chunks(int chunks) {
   return worst;
 }
 
-// Start of output row `token`: in y, or (tensor-parallel push) in the landing rows of the rank that owns it.
-__device__ __forceinline__ uint16_t* out_row(const GemmParams& p, long long token) {
-  if (p.push_tp == 0) return reinterpret_cast<uint16_t*>(p.y) + token * p.ldy;
-  return p.push_dst[(int)token / p.push_rows] + token * p.ldy;
-}
-
-__device__ __forceinline__ void store_elem(const GemmParams& p, uint16_t* row, int col, float v) {
+__device__ __forceinline__ void store_out(const GemmParams& p, long long token, int col, float v) {
   if (p.out_f16)
-    reinterpret_cast<__half*>(row)[col] = __float2half_rn(v);
+    reinterpret_cast<__half*>(p.y)[token * p.ldy + col] = __float2half_rn(v);
   else
-    reinterpret_cast<__nv_bfloat16*>(row)[col] = __float2bfloat16_rn(v);
-}
-
-// Tensor-parallel push: ONE thread calls this after a barrier that orders the stores of tokens
-// [tok_lo, tok_hi) x `cols` columns before it.  The system-scope fence makes those stores visible to the
-// owners before the counts that announce them.
-__device__ __forceinline__ void push_signal(const GemmParams& p, int tok_lo, int tok_hi, int cols) {
-  if (p.push_tp == 0 || cols <= 0) return;
-  if (tok_hi > p.m) tok_hi = p.m;
-  if (tok_lo >= tok_hi) return;
-  __threadfence_system();
-  for (int owner = tok_lo / p.push_rows; owner < p.push_tp && owner * p.push_rows < tok_hi; ++owner) {
-    const int lo = tok_lo > owner * p.push_rows ? tok_lo : owner * p.push_rows;
-    const int hi = tok_hi < (owner + 1) * p.push_rows ? tok_hi : (owner + 1) * p.push_rows;
-    asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p.push_arrived[owner]),
-                 "r"((unsigned)((hi - lo) * cols))
-                 : "memory");
-  }
+    reinterpret_cast<__nv_bfloat16*>(p.y)[token * p.ldy + col] = __float2bfloat16_rn(v);
 }
 
 // Up to 128 tokens.  The 128 UMMA rows are weight rows (one 128-row scale block per tile), the BN columns
@@ -327,28 +298,14 @@ __global__ void __launch_bounds__((kNarrowEpiWarps + 2) * 32, (BN <= 32 ? 2 : 1)
 
   // ---------------- output: direct (split == 1) or reduced across the cluster ----------------
   const int w_row = tw * kTileR + row_in_tile;  // weight row = output column
-  int tok_lo = 0, tok_hi = 0;                  // the tokens this CTA stores (all columns of its weight tile)
   if (split == 1) {
     if (warp < E && w_row < p.n) {
-      // Rows are visited in increasing order: the row start is looked up again only where the owner changes.
-      int boundary = tt * BN;
-      uint16_t* row = nullptr;
 #pragma unroll
       for (int j = 0; j < BN; ++j) {
         const int tok = tt * BN + j;
-        if (tok < p.m) {
-          if (tok == boundary) {
-            row = out_row(p, tok);
-            boundary = p.push_tp == 0 ? p.m : (tok / p.push_rows + 1) * p.push_rows;
-          } else {
-            row += p.ldy;
-          }
-          store_elem(p, row, w_row, acc[j]);
-        }
+        if (tok < p.m) store_out(p, tok, w_row, acc[j]);
       }
     }
-    tok_lo = tt * BN;
-    tok_hi = tt * BN + BN;
   } else {
     // Every MMA of this CTA has completed (the promotion consumed the last accumulator), so the stage ring
     // is free.  Rank d owns the 8-token chunks [d * slice, (d + 1) * slice) of the tile: every CTA pushes
@@ -387,22 +344,16 @@ __global__ void __launch_bounds__((kNarrowEpiWarps + 2) * 32, (BN <= 32 ? 2 : 1)
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const int tok = tt * BN + ch * 8 + j;
-            if (tok < p.m) store_elem(p, out_row(p, tok), w_row, sum[j]);
+            if (tok < p.m) store_out(p, tok, w_row, sum[j]);
           }
         }
       }
     }
     // No CTA reads a peer after the barrier above, so nothing more is needed before exit.
-    tok_lo = tt * BN + rank * slice * 8;
-    tok_hi = tt * BN + ((rank + 1) * slice < kChunks ? (rank + 1) * slice : kChunks) * 8;
   }
 
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) {
-    const int cols = p.n - tw * kTileR;
-    push_signal(p, tok_lo, tok_hi, cols < kTileR ? cols : kTileR);
-  }
   if (warp == E + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -506,7 +457,7 @@ __device__ __forceinline__ void wide_cluster_reduce(const GemmParams& p, uint32_
                                                     int tok0, int col_base) {
   constexpr int kGroups = 64 / kSplit, kItems = kTileR * kGroups / (kWideEpiWarps * 32);
   const int g_lo = kGroups * rank;
-  const bool vec = (p.ldy % 4 == 0) && (p.push_tp > 0 || (reinterpret_cast<uintptr_t>(p.y) & 7) == 0);
+  const bool vec = (p.ldy % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 7) == 0);
   float4 part[kItems][kSplit];
 #pragma unroll
   for (int u = 0; u < kItems; ++u) {
@@ -530,7 +481,7 @@ __device__ __forceinline__ void wide_cluster_reduce(const GemmParams& p, uint32_
     }
     const int tok = tok0 + row, n0 = col_base + g * 4;
     if (tok < p.m && n0 < p.n) {
-      uint16_t* dst = out_row(p, tok) + n0;
+      uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + (long long)tok * p.ldy + n0;
       if (vec && n0 + 4 <= p.n) {
         uint2 w;
         w.x = p.out_f16 ? Mma16816<__half>::pack(sum.x, sum.y) : Mma16816<__nv_bfloat16>::pack(sum.x, sum.y);
@@ -749,20 +700,13 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       const int r_glob = tok0 + row_in_tile;
       if (split == 1) {
         const int n0 = it.tn * BN + col0;
-        const bool vec = (p.ldy % 8 == 0) && (p.push_tp > 0 || (reinterpret_cast<uintptr_t>(p.y) & 15) == 0) &&
-                         (n0 + kCols <= p.n);
+        const bool vec = (p.ldy % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.y) & 15) == 0) && (n0 + kCols <= p.n);
         if (vec) {
           // Rows leave through a per-warp staging area so that global stores are whole 64-byte row
           // segments: a lane parks 32 columns of its own row (4 x 16 bytes, unit u of row r at
           // r * 4 + ((u + r / 2) & 3): conflict-free both ways), then four lanes store one row segment.
           uint4* stage = reinterpret_cast<uint4*>(store_base + warp * 2048);
-          const int row_of_lane = lane >> 2, unit = lane & 3;
-          uint16_t* dst_row[4];  // the four rows this lane stores segments of
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int tok = tok0 + quad * 32 + i * 8 + row_of_lane;
-            dst_row[i] = tok < p.m ? out_row(p, tok) : nullptr;
-          }
+          const int out_row = lane >> 2, unit = lane & 3;
 #pragma unroll
           for (int c = 0; c < kCols; c += 32) {
 #pragma unroll
@@ -778,15 +722,19 @@ __global__ void __launch_bounds__(kWideThreads, 1)
             }
             __syncwarp();
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int r = i * 8 + row_of_lane;
+            for (int r8 = 0; r8 < 32; r8 += 8) {
+              const int r = r8 + out_row;
               const uint4 v = stage[r * 4 + ((unit + (r >> 1)) & 3)];
-              if (dst_row[i] != nullptr) *reinterpret_cast<uint4*>(dst_row[i] + n0 + c + unit * 8) = v;
+              const int tok = tok0 + quad * 32 + r;
+              if (tok < p.m) {
+                uint16_t* dst = reinterpret_cast<uint16_t*>(p.y) + (long long)tok * p.ldy + n0 + c + unit * 8;
+                *reinterpret_cast<uint4*>(dst) = v;
+              }
             }
             __syncwarp();
           }
         } else if (r_glob < p.m) {
-          uint16_t* yrow = out_row(p, r_glob) + n0;
+          uint16_t* yrow = reinterpret_cast<uint16_t*>(p.y) + (long long)r_glob * p.ldy + n0;
 #pragma unroll
           for (int j = 0; j < kCols; ++j) {
             if (n0 + j < p.n) {
@@ -797,8 +745,6 @@ __global__ void __launch_bounds__(kWideThreads, 1)
             }
           }
         }
-        __syncwarp();  // the warp's 32 rows x kCols columns are stored
-        if (lane == 0) push_signal(p, tok0 + quad * 32, tok0 + quad * 32 + 32, p.n - n0 < kCols ? p.n - n0 : kCols);
       } else {
         // Park the partial: float4 (row, g) lives at slot row * 64 + (g ^ (row & 7)), so that both the
         // row-per-lane writes here and the column-group-per-lane reads below are free of bank conflicts.
@@ -815,10 +761,6 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         else
           wide_cluster_reduce<4>(p, smem_u32(stage_base), rank, epi_tid, tok0, it.tn * BN);
         cluster_sync_all();  // no CTA leaves while a peer may still read its partial
-        if (epi_tid == 0) {      // the barrier also put this CTA's stores before the announcement
-          const int width = BN / split, first = it.tn * BN + rank * width;
-          push_signal(p, tok0, tok0 + kTileR, p.n - first < width ? p.n - first : width);
-        }
       }
 #pragma unroll
       for (int j = 0; j < kCols; ++j) acc[j] = 0.f;
@@ -1121,16 +1063,12 @@ extern "C" int mie_fp8_quantize(const void* x, int64_t ldx, int32_t dtype, void*
   return MIE_OK;
 }
 
-namespace {
-
-// The GEMM behind both entry points.  push == nullptr: rows go to y.  Otherwise every output row goes to the
-// landing rows of the rank that owns it (y is not used).
-int run_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8, int64_t ldw,
-                 const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy, int32_t out_dtype, int32_t m,
-                 int32_t n, int32_t k, int32_t max_split, int32_t flags, int32_t* status, void* stream_,
-                 const mie_tp_push_t* push) {
+extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
+                            int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy,
+                            int32_t out_dtype, int32_t m, int32_t n, int32_t k, int32_t max_split, int32_t flags,
+                            int32_t* status, void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  MIE_CHECK_ARG(x8 && a_scale && w8 && w_scale && (y || push), "null pointer");
+  MIE_CHECK_ARG(x8 && a_scale && w8 && w_scale && y, "null pointer");
   MIE_CHECK_ARG(m >= 0 && n >= 1 && k >= 1, "invalid GEMM shape %d x %d x %d", m, n, k);
   MIE_CHECK_ARG(out_dtype == MIE_DTYPE_BF16 || out_dtype == MIE_DTYPE_F16, "output must be bf16 or fp16");
   MIE_CHECK_ARG(ldx % 16 == 0 && ldw % 16 == 0, "operand row strides must be multiples of 16 bytes");
@@ -1168,19 +1106,6 @@ int run_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_sc
   }();
   p.prefetch = prefetch && !(flags & MIE_GEMM_NO_WEIGHT_PREFETCH);
   p.tile_begin = p.tile_end = p.late_wait = 0;
-  p.push_tp = p.push_rows = 0;
-  for (int r = 0; r < MIE_TP_MAX_RANKS; ++r) {
-    p.push_dst[r] = nullptr;
-    p.push_arrived[r] = nullptr;
-  }
-  if (push != nullptr) {
-    p.push_tp = push->tp;
-    p.push_rows = push->rows_per_rank;
-    for (int r = 0; r < push->tp; ++r) {
-      p.push_dst[r] = reinterpret_cast<uint16_t*>(push->rows[r]);
-      p.push_arrived[r] = push->arrived[r];
-    }
-  }
 
   CUtensorMap mw, mx;
   if (narrow) {
@@ -1200,33 +1125,4 @@ int run_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_sc
   if (int rc = operand_map(x8, m, k, ldx, kTileR, &mx)) return rc;
   if (int rc = operand_map(w8, n, k, ldw, kWideBN, &mw)) return rc;
   return launch_wide(mx, mw, p, max_split, stream);
-}
-
-}  // namespace
-
-extern "C" int mie_fp8_gemm(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld, const void* w8,
-                            int64_t ldw, const float* w_scale, int32_t w_scale_ld, void* y, int64_t ldy,
-                            int32_t out_dtype, int32_t m, int32_t n, int32_t k, int32_t max_split, int32_t flags,
-                            int32_t* status, void* stream) {
-  MIE_CHECK_ARG(y != nullptr, "null pointer");
-  return run_fp8_gemm(x8, ldx, a_scale, a_scale_ld, w8, ldw, w_scale, w_scale_ld, y, ldy, out_dtype, m, n, k,
-                      max_split, flags, status, stream, nullptr);
-}
-
-extern "C" int mie_fp8_gemm_tp_push(const void* x8, int64_t ldx, const float* a_scale, int32_t a_scale_ld,
-                                    const void* w8, int64_t ldw, const float* w_scale, int32_t w_scale_ld,
-                                    const mie_tp_push_t* push, int32_t m, int32_t n, int32_t k, int32_t max_split,
-                                    int32_t flags, int32_t* status, void* stream) {
-  MIE_CHECK_ARG(push != nullptr, "null pointer");
-  MIE_CHECK_ARG(push->tp >= 1 && push->tp <= MIE_TP_MAX_RANKS, "%d ranks are out of range", push->tp);
-  MIE_CHECK_ARG(push->ld >= n && push->ld % 8 == 0, "landing rows must hold n columns and be 16-byte aligned");
-  // The owner of row t is t / rows_per_rank: the split mie_tp_reduce_rms_norm_pushed uses for the same m.
-  MIE_CHECK_ARG(push->rows_per_rank >= 1 && (int64_t)push->rows_per_rank * push->tp >= m,
-                "rows_per_rank %d x %d ranks does not cover %d rows", push->rows_per_rank, push->tp, m);
-  for (int r = 0; r < push->tp; ++r) {
-    MIE_CHECK_ARG(push->rows[r] && push->arrived[r], "rank %d: null landing rows or counter", r);
-    MIE_CHECK_ARG((reinterpret_cast<uintptr_t>(push->rows[r]) & 15) == 0, "rank %d: landing rows must be 16-byte aligned", r);
-  }
-  return run_fp8_gemm(x8, ldx, a_scale, a_scale_ld, w8, ldw, w_scale, w_scale_ld, nullptr, push->ld, MIE_DTYPE_BF16, m,
-                      n, k, max_split, flags, status, stream, push);
 }

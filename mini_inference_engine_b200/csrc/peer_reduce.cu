@@ -35,13 +35,7 @@ struct PeerReduceParams {
   float* scales[kMaxRanks];
   __nv_bfloat16* normed[kMaxRanks];
   unsigned* flags[kMaxRanks];  // rank r's flag block: [0..8) "partial ready" epochs, [8] count of rows landed
-  unsigned* state;             // local: [0] last finished epoch, [1] CTA arrival counter, [2] rows landed so far,
-                               //        [3] pushed elements expected before this call
-  // Pushed mode (landing != nullptr): the projections delivered their partial rows into LOCAL memory,
-  // rank s's rows at landing + s * slot_stride, and counted the elements into *arrived.
-  const __nv_bfloat16* landing;
-  long long slot_stride;
-  const unsigned* arrived;
+  unsigned* state;             // local: [0] last finished epoch, [1] CTA arrival counter, [2] rows landed so far
   const __nv_bfloat16* residual;
   __nv_bfloat16* summed;
   const __nv_bfloat16* weight;
@@ -89,18 +83,10 @@ __global__ void __launch_bounds__(1024) peer_reduce_norm_kernel(PeerReduceParams
   chain_release();
   const unsigned epoch = *reinterpret_cast<volatile unsigned*>(p.state) + 1;
 
-  const bool pushed = p.landing != nullptr;
-  const unsigned pushed_now = (unsigned)p.row_count * (unsigned)p.cols * (unsigned)p.tp;
+  // ---- 1. my partial sums are complete (this kernel follows the GEMM in stream order); wait for the peers' ----
+  if (blockIdx.x == 0 && tid < p.tp && tid != p.rank) st_release_sys(p.flags[tid] + p.rank, epoch);
   bool ok = true;
-  if (pushed) {
-    // ---- 1. every rank's projection has delivered its part of the rows this rank owns (its own included) ----
-    const unsigned expected = *reinterpret_cast<volatile unsigned*>(p.state + 3) + pushed_now;
-    if (tid == 0) ok = wait_epoch(p.arrived, expected, p.max_polls);
-  } else {
-    // ---- 1. my partial sums are complete (this kernel follows the GEMM in stream order); wait for the peers' ----
-    if (blockIdx.x == 0 && tid < p.tp && tid != p.rank) st_release_sys(p.flags[tid] + p.rank, epoch);
-    if (tid < p.tp && tid != p.rank) ok = wait_epoch(p.flags[p.rank] + tid, epoch, p.max_polls);
-  }
+  if (tid < p.tp && tid != p.rank) ok = wait_epoch(p.flags[p.rank] + tid, epoch, p.max_polls);
   if (!__syncthreads_and(ok ? 1 : 0) && tid == 0) raise_status(p.status, MIE_STATUS_WAIT_TIMEOUT);
 
   // ---- 2. + 3. reduce, add, normalise and scatter the rows this rank owns ----
@@ -115,8 +101,7 @@ __global__ void __launch_bounds__(1024) peer_reduce_norm_kernel(PeerReduceParams
       uint4 raw[kMaxRanks];
 #pragma unroll
       for (int r = 0; r < kMaxRanks; ++r)
-        if (r < p.tp)
-          raw[r] = ld_volatile_v4((pushed ? p.landing + r * p.slot_stride : p.partial[r]) + row * p.ld_partial + c0);
+        if (r < p.tp) raw[r] = ld_volatile_v4(p.partial[r] + row * p.ld_partial + c0);
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int r = 0; r < kMaxRanks; ++r) {
@@ -192,7 +177,6 @@ __global__ void __launch_bounds__(1024) peer_reduce_norm_kernel(PeerReduceParams
       p.state[1] = 0;
       p.state[0] = epoch;
       p.state[2] += (unsigned)(p.rows - p.row_count);
-      if (pushed) p.state[3] += pushed_now;
     }
   }
 }
@@ -256,14 +240,10 @@ extern "C" int mie_ipc_close(void* mapped, int64_t offset) {
   return MIE_OK;
 }
 
-namespace {
-
-// landing == nullptr: the ranks' partial rows are read from peers->partial (peer loads).  Otherwise they are
-// read from the local landing rows the projections pushed them into.
-int launch_reduce_norm(const mie_tp_peers_t* peers, int32_t tp, int32_t rank, int64_t ld_partial, const void* landing,
-                       int64_t slot_stride, const uint32_t* arrived, const void* residual, void* summed,
-                       const void* weight, int64_t ldq, int32_t scale_ld, int32_t rows, int32_t cols, float eps,
-                       uint32_t* state, uint32_t max_polls, int32_t* status, void* stream) {
+extern "C" int mie_tp_reduce_rms_norm(const mie_tp_peers_t* peers, int32_t tp, int32_t rank, int64_t ld_partial,
+                                      const void* residual, void* summed, const void* weight, int64_t ldq,
+                                      int32_t scale_ld, int32_t rows, int32_t cols, float eps, uint32_t* state,
+                                      uint32_t max_polls, int32_t* status, void* stream) {
   MIE_CHECK_ARG(peers && residual && summed && weight && state, "null pointer");
   MIE_CHECK_ARG(tp >= 1 && tp <= kMaxRanks && rank >= 0 && rank < tp, "rank %d of %d is out of range", rank, tp);
   MIE_CHECK_ARG(rows >= 0 && cols >= 8 && cols % 8 == 0 && cols <= 8192 && ld_partial % 8 == 0 && ld_partial >= cols,
@@ -275,8 +255,7 @@ int launch_reduce_norm(const mie_tp_peers_t* peers, int32_t tp, int32_t rank, in
   PeerReduceParams p;
   for (int r = 0; r < kMaxRanks; ++r) {
     const bool live = r < tp;
-    MIE_CHECK_ARG(!live || ((landing || peers->partial[r]) && peers->flags[r]), "rank %d: null partial or flag pointer",
-                  r);
+    MIE_CHECK_ARG(!live || (peers->partial[r] && peers->flags[r]), "rank %d: null partial or flag pointer", r);
     MIE_CHECK_ARG(!live || !want_q || (peers->q[r] && peers->scales[r]), "rank %d: null quantised output", r);
     MIE_CHECK_ARG(!live || !want_normed || peers->normed[r], "rank %d: null bf16 output", r);
     MIE_CHECK_ARG(!live || ((reinterpret_cast<uintptr_t>(peers->partial[r]) | reinterpret_cast<uintptr_t>(peers->q[r]) |
@@ -294,9 +273,6 @@ int launch_reduce_norm(const mie_tp_peers_t* peers, int32_t tp, int32_t rank, in
   const int begin = per_rank * rank < rows ? per_rank * rank : rows;
   const int end = begin + per_rank < rows ? begin + per_rank : rows;
   p.state = state;
-  p.landing = (const __nv_bfloat16*)landing;
-  p.slot_stride = slot_stride;
-  p.arrived = arrived;
   p.residual = (const __nv_bfloat16*)residual;
   p.summed = (__nv_bfloat16*)summed;
   p.weight = (const __nv_bfloat16*)weight;
@@ -317,28 +293,4 @@ int launch_reduce_norm(const mie_tp_peers_t* peers, int32_t tp, int32_t rank, in
   MIE_CUDA(launch_chained(peer_reduce_norm_kernel, dim3(blocks), dim3(threads), 0, (cudaStream_t)stream, p));
   MIE_LAUNCH_CHECK("peer_reduce_norm_kernel");
   return MIE_OK;
-}
-
-}  // namespace
-
-extern "C" int mie_tp_reduce_rms_norm(const mie_tp_peers_t* peers, int32_t tp, int32_t rank, int64_t ld_partial,
-                                      const void* residual, void* summed, const void* weight, int64_t ldq,
-                                      int32_t scale_ld, int32_t rows, int32_t cols, float eps, uint32_t* state,
-                                      uint32_t max_polls, int32_t* status, void* stream) {
-  return launch_reduce_norm(peers, tp, rank, ld_partial, nullptr, 0, nullptr, residual, summed, weight, ldq, scale_ld,
-                            rows, cols, eps, state, max_polls, status, stream);
-}
-
-extern "C" int mie_tp_reduce_rms_norm_pushed(const mie_tp_peers_t* peers, int32_t tp, int32_t rank,
-                                             const void* landing, int64_t ld_landing, int64_t slot_stride,
-                                             const uint32_t* arrived, const void* residual, void* summed,
-                                             const void* weight, int64_t ldq, int32_t scale_ld, int32_t rows,
-                                             int32_t cols, float eps, uint32_t* state, uint32_t max_polls,
-                                             int32_t* status, void* stream) {
-  MIE_CHECK_ARG(landing && arrived, "null pointer");
-  MIE_CHECK_ARG((reinterpret_cast<uintptr_t>(landing) & 15) == 0 && slot_stride % 8 == 0 &&
-                    slot_stride >= (int64_t)rows * ld_landing,
-                "landing slots must be 16-byte aligned and hold rows x ld_landing elements each");
-  return launch_reduce_norm(peers, tp, rank, ld_landing, landing, slot_stride, arrived, residual, summed, weight, ldq,
-                            scale_ld, rows, cols, eps, state, max_polls, status, stream);
 }

@@ -22,7 +22,6 @@ raises.
 
 from __future__ import annotations
 
-import ctypes
 import os
 from dataclasses import dataclass
 from typing import Any
@@ -224,23 +223,6 @@ def launch_fp8_gemm(quantized: torch.Tensor, scales_kmajor: torch.Tensor, weight
         _lib.ptr(w), w.stride(0), _lib.ptr(scales_w), scales_w.stride(0),
         _lib.ptr(output), output.stride(0), _lib.DTYPE_CODES[output.dtype], m, int(weight.shape[0]), k,
         int(_DEFAULT_MAX_SPLIT if max_split is None else max_split),
-        _lib.GEMM_NO_WEIGHT_PREFETCH if fresh_copy else 0, _lib.ptr(word), _lib.stream_arg(device),
-    ))
-
-
-def launch_fp8_gemm_push(quantized: torch.Tensor, scales_kmajor: torch.Tensor, weight: torch.Tensor,
-                         weight_scale_inv: torch.Tensor, push, m: int, k: int, device: torch.device,
-                         status: torch.Tensor | None = None, max_split: int | None = None) -> None:
-    """``launch_fp8_gemm`` for a row-parallel projection under tensor parallelism: the output rows go to the
-    landing rows ``push`` (a ``_lib.TpPushT``) names instead of a local tensor; ``mie_fp8_gemm_tp_push``."""
-
-    w, fresh_copy = _gemm_weight(weight)
-    scales_w = weight_scale_inv if weight_scale_inv.stride(1) == 1 else weight_scale_inv.contiguous()
-    word = status if status is not None else _lib.status_word(device)
-    _lib.check(_lib.load().mie_fp8_gemm_tp_push(
-        _lib.ptr(quantized), quantized.stride(0), _lib.ptr(scales_kmajor), scales_kmajor.stride(0),
-        _lib.ptr(w), w.stride(0), _lib.ptr(scales_w), scales_w.stride(0), ctypes.byref(push), m,
-        int(weight.shape[0]), k, int(_DEFAULT_MAX_SPLIT if max_split is None else max_split),
         _lib.GEMM_NO_WEIGHT_PREFETCH if fresh_copy else 0, _lib.ptr(word), _lib.stream_arg(device),
     ))
 

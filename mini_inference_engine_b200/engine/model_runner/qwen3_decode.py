@@ -588,12 +588,8 @@ class Qwen3DecodeRunner:
         self._lm_keys = torch.zeros(256, dtype=torch.int64, device=self.device)
         # Tensor parallel decode: the all-reduce after o_proj / down_proj is fused into the residual add +
         # RMSNorm + quantisation kernel over peer memory unless MIE_TP_EXCHANGE=nccl (or fused_exchange=False).
-        mode = os.environ.get("MIE_TP_EXCHANGE", "push")
         if fused_exchange is None:
-            fused_exchange = mode != "nccl"
-        # push: the projection's epilogue delivers its rows to the owners' memory (mie_fp8_gemm_tp_push);
-        # pull (MIE_TP_EXCHANGE=fused): the projection writes locally and the exchange kernel loads from the peers.
-        self.exchange_push = mode != "fused"
+            fused_exchange = os.environ.get("MIE_TP_EXCHANGE", "fused") != "nccl"
         self.exchange = None
         if self.tp > 1 and fused_exchange:
             # Rows for the largest decode bucket plus the largest prompt-chunk bucket of a mixed step; a longer
@@ -663,13 +659,9 @@ class Qwen3DecodeRunner:
         if ex is None or rows > ex.max_rows:
             out = self._all_reduce(self._gemm(quantized, weight, weight_scale, rows, k))
             return self._norm(out, norm_weight, residual, quantize=quantize)
-        if self.exchange_push:
-            ex.push_gemm(quantized, weight, weight_scale, rows, k, status=self.status)
-        else:
-            self._gemm(quantized, weight, weight_scale, rows, k, out=ex.partial[:rows])
+        self._gemm(quantized, weight, weight_scale, rows, k, out=ex.partial[:rows])
         summed = torch.empty_like(residual)
-        ex.reduce_norm(rows, residual, summed, norm_weight, self.shape.rms_eps, quantized=quantize, status=self.status,
-                       pushed=self.exchange_push)
+        ex.reduce_norm(rows, residual, summed, norm_weight, self.shape.rms_eps, quantized=quantize, status=self.status)
         if quantize:
             return None, summed, (ex.q[:rows], ex.scales[:, :rows])
         return ex.normed[:rows], summed, None

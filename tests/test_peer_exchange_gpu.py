@@ -42,7 +42,7 @@ def _close(got: torch.Tensor, want: torch.Tensor, max_mismatch: float = 0.02) ->
 
 
 def _emulated(tp: int, rows: int, cols: int, device):
-    nbytes = PeerExchange.layout(rows, cols, tp)[1]
+    nbytes = PeerExchange.layout(rows, cols)[1]
     blocks = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(tp)]
     return [PeerExchange(tp, r, rows, cols, device, emulated_blocks=blocks) for r in range(tp)]
 
@@ -115,97 +115,6 @@ def test_fused_exchange_equals_library_norm_of_the_reduced_rows_bitwise(device):
     for ex in ranks:
         assert torch.equal(ex.q[:rows].view(torch.uint8), want_q.view(torch.uint8))
         assert torch.equal(ex.scales[:, :rows], want_scales)
-
-
-def _row_parallel_operands(tp, rows, k, cols, seed):
-    """Per rank: quantised activations ``[rows, k]`` (K-major scales) and an e4m3 weight shard ``[cols, k]``."""
-
-    from mini_inference_engine_b200.engine.kernels import sm89_fp8
-
-    generator = torch.Generator().manual_seed(seed)
-    operands = []
-    for rank in range(tp):
-        x = (torch.randn(rows, k, generator=generator) * (0.5 + rank)).to(torch.bfloat16)
-        weight = torch.randn(cols, k, generator=generator) * 0.05
-        operands.append((x, *hot_path.quantize_weight(weight)))
-    return operands, sm89_fp8
-
-
-# (ranks, rows, K of the shard, columns, largest K split): the narrow kernel direct and reduced across a cluster,
-# owners changing inside a token tile, the wide kernel whole-tile (vector stores and a ragged last column tile) and
-# with 2- and 4-CTA cluster reductions, more rows than one tile, a rank without rows.
-PUSH_CASES = [(2, 8, 512, 2560, 1), (2, 8, 2048, 2560, 0), (4, 37, 1024, 2560, 0), (8, 5, 512, 2560, 0),
-              (8, 256, 512, 2560, 1), (8, 256, 512, 2560, 0), (8, 256, 1280, 2560, 0), (2, 768, 2048, 2560, 0),
-              (4, 300, 256, 384, 1), (4, 130, 384, 1536, 0)]
-
-
-@pytest.mark.parametrize("tp,rows,k,cols,max_split", PUSH_CASES)
-def test_pushed_projection_equals_the_pulled_exchange_bitwise(device, tp, rows, k, cols, max_split):
-    """``mie_fp8_gemm_tp_push`` + ``mie_tp_reduce_rms_norm_pushed`` against ``mie_fp8_gemm`` into ``partial`` +
-    ``mie_tp_reduce_rms_norm``: the landing slots hold exactly the owners' rows of every rank's partial sums, the
-    arrival counters exactly the number of elements delivered, and the exchange results are the same bits."""
-
-    operands, sm89_fp8 = _row_parallel_operands(tp, rows, k, cols, seed=tp * 7919 + rows + k)
-    pulled, pushed = _emulated(tp, rows, cols, device), _emulated(tp, rows, cols, device)
-    weight = (torch.randn(cols, generator=torch.Generator().manual_seed(3)) * 0.1 + 1.0).to(torch.bfloat16).to(device)
-    residual = torch.randn(rows, cols, generator=torch.Generator().manual_seed(4)).to(torch.bfloat16).to(device)
-    status = torch.zeros(1, dtype=torch.int32, device=device)
-    split = None if max_split == 0 else max_split
-    delivered = [0] * tp
-    for step in range(2):  # the second pass runs on top of the first one's counters
-        for rank, (x, w8, w_scale) in enumerate(operands):
-            quantized = sm89_fp8.quantize_activation_kmajor((x * (1 + step)).to(device))
-            w8_dev, w_scale_dev = w8.to(device), w_scale.to(device)
-            sm89_fp8.launch_fp8_gemm(quantized[0], quantized[1], w8_dev, w_scale_dev, pulled[rank].partial[:rows], rows,
-                                     k, status=status, max_split=split)
-            pushed[rank].push_gemm(quantized, w8_dev, w_scale_dev, rows, k, status=status, max_split=split)
-        torch.cuda.synchronize(device)
-        for owner, ex in enumerate(pushed):
-            owned = ex.owned_rows(rows)
-            delivered[owner] += len(owned) * cols * tp
-            assert int(ex.flags[PeerExchange.ARRIVED_WORD].item()) == delivered[owner]
-            for source in range(tp):
-                assert torch.equal(ex.landing[source, owned.start:owned.stop],
-                                   pulled[source].partial[owned.start:owned.stop]), (owner, source)
-        for quantized_out in (True, False):
-            got = [torch.zeros(rows, cols, dtype=torch.bfloat16, device=device) for _ in range(2)]
-            for ex in pulled + pushed:  # the peers' epoch flags of the pull form and "rows landed": already signalled
-                ex.flags[:PeerExchange.ARRIVED_WORD].fill_(1 << 20)
-            for ex in pulled:
-                ex.reduce_norm(rows, residual, got[0], weight, EPS, quantized=quantized_out, status=status)
-            for ex in pushed:
-                ex.reduce_norm(rows, residual, got[1], weight, EPS, quantized=quantized_out, status=status, pushed=True)
-            torch.cuda.synchronize(device)
-            assert int(status.item()) == 0
-            assert torch.equal(got[0], got[1])
-            for a, b in zip(pulled, pushed):
-                if quantized_out:
-                    assert torch.equal(a.q[:rows].view(torch.uint8), b.q[:rows].view(torch.uint8))
-                    assert torch.equal(a.scales[:, :rows], b.scales[:, :rows])
-                else:
-                    assert torch.equal(a.normed[:rows], b.normed[:rows])
-            if quantized_out:  # the bf16 form is a second exchange: its projections deliver once more
-                for rank, (x, w8, w_scale) in enumerate(operands):
-                    quantized = sm89_fp8.quantize_activation_kmajor((x * (1 + step)).to(device))
-                    pushed[rank].push_gemm(quantized, w8.to(device), w_scale.to(device), rows, k, status=status,
-                                           max_split=split)
-                for owner, ex in enumerate(pushed):
-                    delivered[owner] += len(ex.owned_rows(rows)) * cols * tp
-
-
-def test_a_pushed_exchange_without_deliveries_times_out_cleanly(device):
-    """No projection has pushed anything: the bounded wait on the arrival counter gives up and reports it."""
-
-    ranks = _emulated(2, 4, 256, device)
-    status = torch.zeros(1, dtype=torch.int32, device=device)
-    weight = torch.ones(256, dtype=torch.bfloat16, device=device)
-    residual = torch.zeros(4, 256, dtype=torch.bfloat16, device=device)
-    ranks[0].flags[:PeerExchange.ARRIVED_WORD].fill_(1 << 20)
-    ranks[0].reduce_norm(4, residual, torch.zeros_like(residual), weight, EPS, quantized=True, status=status,
-                         max_polls=64, pushed=True)
-    torch.cuda.synchronize(device)
-    assert int(status.item()) & _lib.STATUS_WAIT_TIMEOUT
-    assert torch.ones(4, device=device).sum().item() == 4.0
 
 
 def test_a_wait_that_runs_out_sets_the_status_bit_and_returns(device):
@@ -283,29 +192,6 @@ def _two_gpu_worker(rank: int, world: int, port: int, results) -> None:
                 diff = (ex.normed[:rows].cpu().float() - want_normed.float()).abs()
                 ok &= bool((diff <= want_normed.float().abs().clamp_min(1e-30) * 2.0 ** -7).all())
             residual = want_summed
-        # The push form over real peer memory: the projection's epilogue stores into the other GPU's landing rows
-        # and the exchange kernel waits on its local arrival counter.  Same operands through the pull form first.
-        operands, sm89_fp8 = _row_parallel_operands(world, rows, 1024, cols, seed=5)
-        x, w8, w_scale = operands[rank]
-        w8, w_scale = w8.to(device), w_scale.to(device)
-        residual_dev, weight_dev = residual.to(device), weight.to(device)
-        for step in range(3):
-            quantized = sm89_fp8.quantize_activation_kmajor((x * (1 + step)).to(device))
-            sm89_fp8.launch_fp8_gemm(quantized[0], quantized[1], w8, w_scale, ex.partial[:rows], rows, 1024, status=status)
-            pulled_sum = torch.zeros(rows, cols, dtype=torch.bfloat16, device=device)
-            ex.reduce_norm(rows, residual_dev, pulled_sum, weight_dev, EPS, quantized=True, status=status)
-            torch.cuda.synchronize(device)
-            pulled_q, pulled_scales = ex.q[:rows].view(torch.uint8).clone(), ex.scales[:, :rows].clone()
-            ex.q.view(torch.uint8).zero_()
-            dist.barrier()  # nobody's next exchange lands in q before it was cleared everywhere
-            ex.push_gemm(quantized, w8, w_scale, rows, 1024, status=status)
-            pushed_sum = torch.zeros(rows, cols, dtype=torch.bfloat16, device=device)
-            ex.reduce_norm(rows, residual_dev, pushed_sum, weight_dev, EPS, quantized=True, status=status, pushed=True)
-            torch.cuda.synchronize(device)
-            ok &= torch.equal(pushed_sum, pulled_sum)
-            ok &= torch.equal(ex.q[:rows].view(torch.uint8), pulled_q) and torch.equal(ex.scales[:, :rows], pulled_scales)
-            ok &= bool(pulled_q.any())
-            dist.barrier()
         ok &= int(status.item()) == 0
         results[rank] = bool(ok)
         dist.barrier()
