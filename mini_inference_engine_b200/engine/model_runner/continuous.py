@@ -14,11 +14,17 @@ Two step policies:
 * ``mixed=True``   every iteration is ONE captured forward that carries the decode rows and the prompt chunks
   in one flat token stream (token-count buckets), so a long prompt advances a bounded chunk per step
   instead of stalling decode.
+
+``prefix_cache=True`` lets a request borrow the whole pages of a prompt prefix that another request has already
+written (the reference switches its decode graphs OFF when prefix reuse is on,
+engine/serving/chunked_prefill.py:126-127; here a shared page is just the same id in two block-table rows, so
+the captured decode and mixed steps run unchanged).  Pages are reference-counted; a prefix page nobody uses
+stays cached until the pool needs it back.
 """
 
 from __future__ import annotations
 
-from collections import deque
+from collections import OrderedDict, deque
 from dataclasses import dataclass, field
 
 import torch
@@ -74,6 +80,8 @@ class _Request:
     promised: int = 0          # pages promised and not taken yet
     prefilled: int = 0         # prompt tokens whose K/V are in the cache
     generated: list[int] = field(default_factory=list)
+    borrowed: int = 0          # leading pages taken over from the prefix cache at admission
+    published: int = 0         # leading whole prompt pages already offered to the prefix cache
 
     @property
     def decoding(self) -> bool:
@@ -90,10 +98,17 @@ class ContinuousBatcher:
     ``run()`` drains everything and returns each request's tokens."""
 
     def __init__(self, runner: Qwen3DecodeRunner, *, max_prefill_tokens: int = 512, mixed: bool = False,
-                 use_graphs: bool = True) -> None:
+                 use_graphs: bool = True, prefix_cache: bool = False) -> None:
         if max_prefill_tokens < 1:
             raise ValueError("max_prefill_tokens must be positive")
         self.runner, self.mixed, self.use_graphs = runner, bool(mixed), bool(use_graphs)
+        self.prefix_cache = bool(prefix_cache)
+        # Prefix cache: key of a whole-page prompt prefix -> the page that holds its last 16 tokens.  A key is the
+        # nested tuple (key of the prefix one page shorter, this page's tokens): equal keys mean equal prefixes.
+        self._prefix_pages: OrderedDict[tuple, int] = OrderedDict()
+        self._page_key: dict[int, tuple] = {}
+        self._refs: dict[int, int] = {}  # page -> live requests that have it in their block list
+        self.prefix_hits = 0             # prompt tokens that were not prefilled again
         self.max_prefill_tokens = int(max_prefill_tokens)
         if self.mixed:
             self.max_prefill_tokens = min(self.max_prefill_tokens, max(runner.chunk_buckets))
@@ -115,15 +130,57 @@ class ContinuousBatcher:
             raise ValueError(f"duplicate request id {rid!r}")
         self.waiting.append(_Request(rid, prompt, int(max_new_tokens)))
 
+    def _prefix_keys(self, request: _Request, pages: int):
+        """Keys of the request's first ``pages`` whole prompt pages, shortest prefix first."""
+
+        page, key = self.runner.shape.page, ()
+        for k in range(pages):
+            key = (key, tuple(request.prompt[k * page:(k + 1) * page]))
+            yield key
+
+    def _cached_prefix(self, request: _Request) -> list[int]:
+        """Pages of the longest cached whole-page prefix of the prompt.  At least one prompt token is left to
+        prefill: its logits give the request's first new token."""
+
+        hits = []
+        for key in self._prefix_keys(request, (len(request.prompt) - 1) // self.runner.shape.page):
+            cached = self._prefix_pages.get(key)
+            if cached is None:
+                break
+            hits.append(cached)
+        return hits
+
+    def _evict(self, wanted: int, keep: set[int]) -> None:
+        """Hand cached prefix pages nobody uses back to the pool, oldest first, until ``wanted`` can be promised."""
+
+        for key, cached in list(self._prefix_pages.items()):
+            if self.pool.can_promise(wanted):
+                return
+            if self._refs.get(cached, 0) == 0 and cached not in keep:
+                del self._prefix_pages[key]
+                del self._page_key[cached]
+                self._refs.pop(cached, None)
+                self.pool.give_back([cached], 0)
+
     def _admit(self) -> None:
         page = self.runner.shape.page
         while self.waiting and len(self.live) < self.runner.max_batch:
             request = self.waiting[0]
-            needed = -(-(len(request.prompt) + request.max_new_tokens) // page)
+            hits = self._cached_prefix(request) if self.prefix_cache else []
+            needed = -(-(len(request.prompt) + request.max_new_tokens) // page) - len(hits)
+            if not self.pool.can_promise(needed):
+                self._evict(needed, set(hits))
             if not self.pool.can_promise(needed):
                 break  # FIFO: a large request at the head waits for pages, nothing overtakes it
             self.pool.promise(needed)
             request.promised = needed
+            for cached in hits:
+                self._refs[cached] = self._refs.get(cached, 0) + 1
+                self._prefix_pages.move_to_end(self._page_key[cached])
+            request.pages = list(hits)
+            request.borrowed = request.published = len(hits)
+            request.prefilled = len(hits) * page
+            self.prefix_hits += request.prefilled
             self.live.append(self.waiting.popleft())
 
     def _grow(self, request: _Request, tokens: int) -> None:
@@ -131,18 +188,48 @@ class ContinuousBatcher:
 
         page = self.runner.shape.page
         while len(request.pages) * page < tokens:
-            request.pages.append(self.pool.take())
+            fresh = self.pool.take()
+            request.pages.append(fresh)
+            self._refs[fresh] = 1
             request.promised -= 1
+
+    def _publish(self, request: _Request) -> None:
+        """Offer the whole prompt pages this request has finished writing to the prefix cache."""
+
+        whole = min(request.prefilled, len(request.prompt)) // self.runner.shape.page
+        if whole <= request.published:
+            return
+        for k, key in enumerate(self._prefix_keys(request, whole)):
+            if k >= request.published and key not in self._prefix_pages:
+                self._prefix_pages[key] = request.pages[k]
+                self._page_key[request.pages[k]] = key
+        request.published = whole
 
     def _retire(self) -> None:
         still = []
         for request in self.live:
             if request.decoding and request.finished:
                 self.results[request.rid] = list(request.generated)
-                self.pool.give_back(request.pages, request.promised)
+                private = []
+                for used in request.pages:
+                    self._refs[used] -= 1
+                    if self._refs[used] == 0 and used not in self._page_key:
+                        del self._refs[used]
+                        private.append(used)  # cached prefix pages stay out of the free list until evicted
+                self.pool.give_back(private, request.promised)
             else:
                 still.append(request)
         self.live = still  # order kept: rows are compacted, not shuffled
+
+    def drop_prefix_cache(self) -> None:
+        """Give every cached prefix page that no live request uses back to the pool."""
+
+        for key, cached in list(self._prefix_pages.items()):
+            if self._refs.get(cached, 0) == 0:
+                del self._prefix_pages[key]
+                del self._page_key[cached]
+                self._refs.pop(cached, None)
+                self.pool.give_back([cached], 0)
 
     # -- one iteration ------------------------------------------------------------------------------
 
@@ -197,6 +284,8 @@ class ContinuousBatcher:
             produced.append((request.rid, int(token)))
         for (request, start, count), token in zip(chunks, chunk_tokens):
             request.prefilled = start + count
+            if self.prefix_cache:
+                self._publish(request)
             if request.decoding:  # the chunk completed the prompt: its last row gave the first new token
                 request.generated.append(int(token))
                 produced.append((request.rid, int(token)))

@@ -145,3 +145,42 @@ def test_bucket_graph_equals_the_eager_step_bit_for_bit(device):
     assert torch.equal(runner.key_blocks.index_select(1, live), eager.key_blocks.index_select(1, live))
     assert torch.equal(runner.value_blocks.index_select(1, live), eager.value_blocks.index_select(1, live))
     runner.check_status()
+
+
+@pytest.mark.parametrize("mixed", [False, True])
+def test_requests_sharing_prefix_pages_run_through_the_captured_steps(mixed, device):
+    """Prefix reuse with the graphs ON (the reference turns its decode graphs off under prefix reuse,
+    engine/serving/chunked_prefill.py:126-127): "b" and "c" arrive while "a" decodes, borrow the whole pages of
+    the prompt prefix they have in common with it - the same page ids in several block-table rows of the
+    bucket graphs and of the captured mixed steps - and prefill only their tails.  Tokens equal the oracle's."""
+
+    cpu_weights = Qwen3Weights(SHAPE, torch.device("cpu"), seed=36)
+    generator = torch.Generator().manual_seed(0)
+    common = torch.randint(0, SHAPE.vocab, (48,), generator=generator).tolist()
+    requests = [("a", common + torch.randint(0, SHAPE.vocab, (9,), generator=generator).tolist(), 10),
+                ("b", common + torch.randint(0, SHAPE.vocab, (20,), generator=generator).tolist(), 6),
+                ("c", common[:16] + torch.randint(0, SHAPE.vocab, (30,), generator=generator).tolist(), 5)]
+    expected = _oracle(cpu_weights, requests)
+    runner = Qwen3DecodeRunner(cpu_weights.to(device), num_pages=24, max_batch=4, max_context=128, max_chunks=4,
+                               chunk_buckets=(128,))
+    batcher = ContinuousBatcher(runner, max_prefill_tokens=128, mixed=mixed, prefix_cache=True)
+    batcher.submit(*requests[0])
+    for _ in range(3):
+        batcher.step()
+    donor = batcher.live[0]
+    assert donor.decoding and donor.published == 3
+    batcher.submit(*requests[1])
+    batcher.submit(*requests[2])
+    batcher.step()
+    by_id = {r.rid: r for r in batcher.live}
+    assert by_id["b"].pages[:3] == donor.pages[:3] and by_id["c"].pages[:1] == donor.pages[:1]
+    assert batcher.prefix_hits == 48 + 16
+    results = batcher.run()
+    for rid, _, _ in requests:
+        assert results[rid] == expected[rid], rid
+    assert int(runner.status.item()) == 0
+    kinds = {r["kind"] for r in batcher.records}
+    assert ("mixed" in kinds) if mixed else ("decode+prefill" in kinds)
+    batcher.drop_prefix_cache()
+    assert batcher.pool.free_pages == runner.num_pages
+

@@ -235,3 +235,68 @@ def test_batcher_waits_for_pages_in_fifo_order():
     stuck.submit("never", [1] * 40, 8)  # needs 3 pages, the pool has 2
     with pytest.raises(PagePoolExhausted):
         stuck.run()
+
+
+class _PrefixStubRunner(_StubRunner):
+    """Tokens do not matter here; records every chunk it is asked to prefill."""
+
+    def __init__(self, **kwargs):
+        super().__init__(**kwargs)
+        self.chunks = []
+
+    def _chunk_tokens(self, chunk_items):
+        for tokens, start, pages in chunk_items:
+            assert len(pages) * self.shape.page >= start + len(tokens)
+            self.chunks.append((start, len(tokens), tuple(pages)))
+        return [1] * len(chunk_items)
+
+
+@pytest.mark.parametrize("mixed", [False, True])
+def test_prefix_cache_shares_whole_prompt_pages_and_counts_references(mixed):
+    runner = _PrefixStubRunner(num_pages=16, max_batch=4, max_context=128)
+    batcher = ContinuousBatcher(runner, max_prefill_tokens=32, mixed=mixed, prefix_cache=True)
+    common = list(range(100, 140))                      # 40 tokens: two whole pages and a half
+    batcher.submit("a", common + [1, 2, 3], 6)
+    while not any(r.rid == "a" and r.decoding for r in batcher.live):
+        batcher.step()
+    donor = next(r for r in batcher.live if r.rid == "a")
+    assert donor.published == 2 and donor.borrowed == 0
+    batcher.submit("b", common + [7, 8], 3)            # same first two pages, another tail
+    batcher.submit("c", common[:16] + [9] * 20, 2)     # only the first page in common
+    batcher.submit("d", common[:32], 2)                # the prompt IS two whole pages: one token is left to prefill
+    batcher.step()
+    taker = {r.rid: r for r in batcher.live}
+    assert taker["b"].pages[:2] == donor.pages[:2] and taker["b"].borrowed == 2
+    assert taker["c"].pages[:1] == donor.pages[:1] and taker["c"].borrowed == 1
+    assert taker["d"].pages[:1] == donor.pages[:1] and taker["d"].borrowed == 1
+    assert batcher.prefix_hits == 32 + 16 + 16
+    # The borrowed tokens were never prefilled again: b, c and d start their first chunk behind the shared pages.
+    starts = {pages[:1] + (start,) for start, _, pages in runner.chunks}
+    assert (donor.pages[0], 32) in starts and (donor.pages[0], 16) in starts
+    # Nobody ever writes a position inside a page it borrowed.
+    for request in taker.values():
+        assert request.prefilled >= request.borrowed * 16
+    results = batcher.run()
+    assert set(results) == {"a", "b", "c", "d"}
+    # Private pages are free again; the published prefix pages stay cached until dropped or evicted.
+    cached = set(batcher._prefix_pages.values())
+    assert donor.pages[0] in cached and donor.pages[1] in cached
+    assert batcher.pool.free_pages == runner.num_pages - len(cached)
+    assert all(count == 0 for count in batcher._refs.values())
+    batcher.drop_prefix_cache()
+    assert batcher.pool.free_pages == runner.num_pages and not batcher._prefix_pages
+
+
+def test_cached_prefix_pages_are_evicted_when_the_pool_needs_them():
+    runner = _PrefixStubRunner(num_pages=8, max_batch=2, max_context=128)
+    batcher = ContinuousBatcher(runner, max_prefill_tokens=64, prefix_cache=True)
+    batcher.submit("a", list(range(48)) + [5], 2)       # 4 pages, 3 of them whole prompt pages
+    batcher.run()
+    assert batcher.pool.free_pages == 8 - 3 and len(batcher._prefix_pages) == 3
+    batcher.submit("big", [7] * 100, 20)                # 8 pages: only fits once the cache lets go
+    results = batcher.run()
+    assert "big" in results and len(results["big"]) == 20
+    assert not any(key[1] == tuple(range(16)) for key in batcher._prefix_pages)  # a's pages were reclaimed
+    batcher.drop_prefix_cache()
+    assert batcher.pool.free_pages == 8
+
