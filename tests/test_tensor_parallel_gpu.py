@@ -27,8 +27,8 @@ WEIGHT_SEED, PROMPT_SEED = 82, 0
 PLAN = ((21, 8), (70, 6), (9, 10))
 
 
-def _requests():
-    generator = torch.Generator().manual_seed(PROMPT_SEED)
+def _requests(prompt_seed: int = PROMPT_SEED):
+    generator = torch.Generator().manual_seed(prompt_seed)
     return [(f"r{i}", torch.randint(0, SHAPE.vocab, (n,), generator=generator).tolist(), new)
             for i, (n, new) in enumerate(PLAN)]
 
@@ -39,7 +39,8 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker(rank: int, world: int, port: int, results, mixed: bool) -> None:
+def _worker(rank: int, world: int, port: int, results, mixed: bool, kv_dtype: str = "bf16",
+            weight_seed: int = WEIGHT_SEED, prompt_seed: int = PROMPT_SEED) -> None:
     import torch.distributed as dist
 
     from mini_inference_engine_b200.engine.model_runner.continuous import ContinuousBatcher
@@ -52,12 +53,12 @@ def _worker(rank: int, world: int, port: int, results, mixed: bool) -> None:
     outcome = None
     try:
         # Drawn on the CPU so that the shards are slices of exactly the model the parent's oracle runs.
-        weights = Qwen3Weights(SHAPE, torch.device("cpu"), seed=WEIGHT_SEED, tp_rank=rank, tp_size=world).to(device)
+        weights = Qwen3Weights(SHAPE, torch.device("cpu"), seed=weight_seed, tp_rank=rank, tp_size=world).to(device)
         runner = Qwen3DecodeRunner(weights, num_pages=32, max_batch=4, max_context=128,
-                                   process_group=dist.group.WORLD)
+                                   process_group=dist.group.WORLD, kv_dtype=kv_dtype)
         assert runner.exchange is not None
         batcher = ContinuousBatcher(runner, max_prefill_tokens=128, mixed=mixed)
-        first, late, third = _requests()
+        first, late, third = _requests(prompt_seed)
         batcher.submit(*first)
         batcher.submit(*third)
         for _ in range(3):
@@ -82,24 +83,13 @@ def _worker(rank: int, world: int, port: int, results, mixed: bool) -> None:
         os._exit(0 if outcome and "error" not in outcome else 1)
 
 
-@pytest.mark.parametrize("mixed", [False, True])
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_every_rank_matches_the_unsharded_oracle(world, mixed):
-    if torch.cuda.device_count() < world:
-        pytest.skip(f"needs {world} GPUs")
+def _run_ranks(world: int, worker_args: tuple) -> list:
     import torch.multiprocessing as mp
-
-    cpu = Qwen3Weights(SHAPE, torch.device("cpu"), seed=WEIGHT_SEED)
-    expected = {}
-    for rid, prompt, new in _requests():
-        tokens, margin = oracle_generate(cpu, SHAPE, prompt, new)
-        assert margin >= 0.08, f"the oracle itself is not decisive: margin {margin:.4f}"
-        expected[rid] = tokens
 
     ctx = mp.get_context("spawn")
     results = ctx.Manager().dict()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(rank, world, port, results, mixed)) for rank in range(world)]
+    procs = [ctx.Process(target=_worker, args=(rank, world, port, results, *worker_args)) for rank in range(world)]
     for proc in procs:
         proc.start()
     for proc in procs:
@@ -110,6 +100,22 @@ def test_every_rank_matches_the_unsharded_oracle(world, mixed):
             pytest.fail("a rank did not finish in time")
     outcomes = [results.get(rank) for rank in range(world)]
     assert all(o is not None and "error" not in o for o in outcomes), outcomes
+    return outcomes
+
+
+@pytest.mark.parametrize("mixed", [False, True])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_every_rank_matches_the_unsharded_oracle(world, mixed):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    cpu = Qwen3Weights(SHAPE, torch.device("cpu"), seed=WEIGHT_SEED)
+    expected = {}
+    for rid, prompt, new in _requests():
+        tokens, margin = oracle_generate(cpu, SHAPE, prompt, new)
+        assert margin >= 0.08, f"the oracle itself is not decisive: margin {margin:.4f}"
+        expected[rid] = tokens
+
+    outcomes = _run_ranks(world, (mixed,))
     for rank, outcome in enumerate(outcomes):
         assert outcome["status"] == 0, (rank, outcome["status"])
         assert outcome["replays"] >= 4
@@ -118,3 +124,33 @@ def test_every_rank_matches_the_unsharded_oracle(world, mixed):
         assert outcome["tokens"] == expected, (rank, outcome["tokens"], expected)
     if world == 8:  # odd ranks start in the middle of a scale block
         assert outcomes[1]["window"] == (256, 64, 192) and outcomes[0]["window"] == (256, 0, 192)
+
+
+KV8_WEIGHT_SEED, KV8_PROMPT_SEED, KV8_MARGIN = 226, 0, 0.1
+
+
+@pytest.mark.parametrize("mixed", [False, True])
+@pytest.mark.parametrize("world", [2, 4])
+def test_fp8_kv_cache_under_tensor_parallelism(world, mixed):
+    """The opt-in FP8 KV cache with sharded KV heads: every rank quantises the rows of its own heads (one scale
+    per token and KV head, so sharding does not change a single byte), prompt chunks attend the staged pages,
+    decode rows the FP8 kernel.  Expected tokens: the unsharded oracle storing every K/V row through the
+    quantise -> dequantise image; its own margin is re-checked before the tokens are compared with ``==``."""
+
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    from oracle import hot_path
+
+    def image(rows):
+        return hot_path.dequantize_kv_rows(*hot_path.quantize_kv_rows(rows))
+
+    cpu = Qwen3Weights(SHAPE, torch.device("cpu"), seed=KV8_WEIGHT_SEED)
+    expected = {}
+    for rid, prompt, new in _requests(KV8_PROMPT_SEED):
+        tokens, margin = oracle_generate(cpu, SHAPE, prompt, new, kv_image=image)
+        assert margin >= KV8_MARGIN, f"the oracle itself is not decisive: margin {margin:.4f}"
+        expected[rid] = tokens
+    outcomes = _run_ranks(world, (mixed, "fp8", KV8_WEIGHT_SEED, KV8_PROMPT_SEED))
+    for rank, outcome in enumerate(outcomes):
+        assert outcome["status"] == 0, (rank, outcome["status"])
+        assert outcome["tokens"] == expected, (rank, outcome["tokens"], expected)
