@@ -61,7 +61,13 @@ def decode(args, device) -> dict:
         lengths = workloads.lognormal_contexts(args.concurrency, seed=args.concurrency)
     total = int(lengths.sum())
     pages = sum(-(-int(n) // workloads.PAGE) for n in lengths) + 8
-    tables = workloads.random_block_tables(lengths, num_pages=pages, seed=1).to(device)
+    tables = workloads.random_block_tables(lengths, num_pages=pages, seed=1)
+    if getattr(args, "sequential_tables", False):
+        # Every request's pages in ascending order, requests back to back: the placement a fresh allocator gives,
+        # against the random placement the benchmark (and the reference's own benchmarks) use.
+        live = tables >= 0
+        tables[live] = torch.arange(int(live.sum()), dtype=tables.dtype)
+    tables = tables.to(device)
     kv_heads, q_heads = workloads.KV_HEADS // args.tp, workloads.Q_HEADS // args.tp
     query = torch.randn(args.concurrency, q_heads, 1, 128, device=device).to(torch.bfloat16)
     out = torch.empty_like(query)
@@ -194,6 +200,8 @@ def main() -> None:
     p.add_argument("--tp", type=int, default=1)
     p.add_argument("--split-policy", type=int, default=1)
     p.add_argument("--kv-dtype", default="bf16", choices=["bf16", "fp8"])
+    p.add_argument("--sequential-tables", action="store_true",
+                   help="pages of a request in ascending order instead of randomly placed")
     p.add_argument("--reuse-plan", action="store_true",
                    help="time decode + merge only, with the plan built once as inside a model step")
     p.add_argument("--lengths", type=lambda text: [int(n) for n in text.split(",")], default=None,
